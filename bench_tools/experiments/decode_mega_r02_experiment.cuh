@@ -469,7 +469,7 @@ __device__ __forceinline__ MkRows mk_gemv_core(MkRing &rg, const MkGeom &g, int 
     if (RPW == 1 && nvec > 96 && !g.no_fast) {
       // ---- fast path (every production shape: one row slice of 97..128 vectors per warp per stage) -------------
       // The round-1 loop was latency-bound, not HBM-bound (trace r02: 0.5-0.66 us of consumer time per 32 KB stage
-      // with < 10 % of it spent waiting for data; SASS: the four LDS.128 of a row went through ONE register quad, and
+      // with < 10 % of it spent waiting for data; the four LDS.128 of a row went through ONE register quad, and
       // every stage ended in a dependent 5-step shuffle tree).  Here (a) the next stage's four vectors are loaded
       // BEFORE the current stage's FMAs are issued (two register sets, software pipelining across stages), (b) a
       // stage is released as soon as its data is in registers, and (c) the lane partials of four consecutive

@@ -36,7 +36,7 @@ if [[ "$what" == ncu || "$what" == all ]]; then
   step "ncu launch list + full capture of the decode kernel (numbers under ncu are never bench values)"
   timeout 600 ncu --metrics gpu__time_duration.sum --clock-control none -c 200 --csv --log-file "$out/launches.csv" \
       python bench.py --gpus 1 --steps 2 --warmup 1 --e2e-steps 2 --no-cpu > "$out/ncu_bench.log" 2>&1
-  timeout 900 ncu --set full --clock-control none --import-source on -k regex:decode_mega_kernel -c 1 -o "$out/mega_full" -f \
+  timeout 900 ncu --set full --clock-control none -k regex:decode_mega_kernel -c 1 -o "$out/mega_full" -f \
       python bench.py --gpus 1 --steps 2 --warmup 1 --e2e-steps 2 --no-cpu >> "$out/ncu_bench.log" 2>&1
   ls -la "$out" | tee -a "$out/round.log"
 fi

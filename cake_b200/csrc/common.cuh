@@ -103,7 +103,7 @@ __device__ __forceinline__ uint64_t policy_evict_last() {
   asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
   return p;
 }
-// TMA 1-D bulk copy global -> shared, completion on an mbarrier (SASS: UBLKCP).  bytes % 16 == 0,
+// TMA 1-D bulk copy global -> shared, completion on an mbarrier.  bytes % 16 == 0,
 // both addresses 16-byte aligned.
 __device__ __forceinline__ void bulk_g2s(void *dst_smem, const void *src_gmem, uint32_t bytes, uint64_t *bar,
                                          uint64_t policy) {

@@ -4,7 +4,7 @@
 // HBM streaming, not math:
 //   * persistent grid, one CTA per SM (148); each CTA owns a contiguous row range [r0,r1) so the
 //     weight bytes of a CTA are ONE contiguous stream (row-major W) — perfectly sequential DRAM pages;
-//   * a dedicated producer warp issues TMA 1-D bulk copies (cp.async.bulk, SASS UBLKCP) of 14-32 KB
+//   * a dedicated producer warp issues TMA 1-D bulk copies (cp.async.bulk) of 14-32 KB
 //     row blocks into a shared-memory ring guarded by full/empty mbarriers; ~80-100 KB in flight
 //     per SM with zero register cost, L2 policy evict_first (each weight byte is used once per token);
 //   * the producer starts streaming BEFORE griddepcontrol.wait: weights do not depend on the previous
