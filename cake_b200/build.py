@@ -39,9 +39,11 @@ def stale() -> bool:
     return any(os.path.getmtime(s) > t for s in sources())
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False, host: bool = True, quiet: bool = False) -> str:
+    """``host=False``: only the library (what the Python host needs); ``quiet``: the compiler's output goes to stderr."""
     if not force and not stale():
-        build_host()
+        if host:
+            build_host()
         return SO
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
     cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
@@ -51,8 +53,12 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")
-    subprocess.check_call(cmd)
-    build_host(force=True)
+    tmp = SO + f".{os.getpid()}.tmp"   # written beside the target and renamed: a concurrent reader never maps half a library
+    cmd[cmd.index("-o") + 1] = tmp
+    subprocess.check_call(cmd, stdout=sys.stderr if quiet else None)
+    os.replace(tmp, SO)
+    if host:
+        build_host(force=True)
     return SO
 
 

@@ -79,6 +79,23 @@ class CBlockVariant(ctypes.Structure):
 SYMBOLS += [("cake_b200_block_set_variant", _I, [_VP, POINTER(CBlockVariant)])]
 
 
+class CLayerSpec(ctypes.Structure):
+    """``cake_b200_layer_spec`` (include/cake_b200.h)."""
+    _fields_ = [("heads", c_int), ("kv_heads", c_int), ("head_dim", c_int), ("window", c_int), ("scale", c_float),
+                ("softcap", c_float), ("values_are_keys", c_int), ("ff", c_int), ("act", c_int), ("scalar_norm", c_int)]
+
+
+class CLayerTensors(ctypes.Structure):
+    """``cake_b200_layer_tensors`` (include/cake_b200.h)."""
+    _fields_ = [(n, _VP) for n in ("norm", "shift", "q", "k", "v", "o", "r1", "r2", "gate", "ff_gate", "ff_up", "ff_down")]
+
+
+SYMBOLS += [
+    ("cake_b200_block_load_spec", _I, [_VP, _I, POINTER(CLayerSpec), POINTER(CLayerTensors), POINTER(_VP)]),
+    ("cake_b200_logits_rows", _I, [_VP, _VP, _I, POINTER(_I), _I, _VP]),
+]
+
+
 class CakeB200Error(RuntimeError):
     def __init__(self, code: int, msg: str):
         super().__init__(f"cake_b200 error {code}: {msg}")

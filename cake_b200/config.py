@@ -31,6 +31,21 @@ class RopeScaling:
 
 
 @dataclass
+class LayerSpec:
+    """One entry of a layer-list config (``cake_b200_layer_spec`` in include/cake_b200.h): a parallel block whose mixer is
+    grouped-query attention with a score soft cap, a distance bias, a sliding window, keys used as values and a per-head
+    output gate, next to an optional gated feed-forward.  Every size and constant is per layer."""
+    heads: int
+    kv_heads: int
+    head_dim: int
+    window: int = 0          # position i sees j with 0 <= i - j < window; 0 = all j <= i
+    scale: float = 1.0
+    softcap: float = 0.0     # 0 = none
+    ff: int = 0              # 0 = the layer has no feed-forward
+    act: int = 1             # 0 silu, 1 tanh-gelu
+
+
+@dataclass
 class Config:
     hidden_size: int
     intermediate_size: int
@@ -57,7 +72,10 @@ class Config:
     residual_rms_norm: bool = False   # config.rs:113: norm weights stored as deltas; (1 + w) in f32 at LOAD time (config.rs:155-173)
     pre_reshape_qk_norm: bool = False  # config.rs:116 (OLMo2): QK-norm over the whole q / k projection, before the head reshape
     global_layers: list = field(default_factory=list)  # config.rs:126-130: per-layer schedule, True = global (full context)
-    block_kind: str = "llama"         # which block.rs the layers are: "llama" (transformer.rs), "olmo2", "gemma3", "exaone4"
+    block_kind: str = "llama"         # which block.rs the layers are: "llama" (transformer.rs), "olmo2", "gemma3", "exaone4";
+                                      # "nigenex": a layer-list model (``layers`` below), not a reference block
+    layers: list = field(default_factory=list)  # layer-list models: one LayerSpec per layer (sizes differ between layers)
+    logit_softcap: float = 0.0        # logits <- cap * tanh(logits / cap) after the head (0 = none)
 
     def layer_variant(self, i: int, max_seq: Optional[int] = None) -> dict:
         """Norm placement and attention mode of layer ``i``, as the reference's per-architecture block.rs sets them up:
@@ -87,6 +105,18 @@ class Config:
         return self.block_kind == "llama"
 
     @property
+    def layer_list(self) -> bool:
+        """The checkpoint's config lists its layers one by one; such models keep an fp32 residual stream."""
+        return self.block_kind == "nigenex"
+
+    def head_tensor_names(self):
+        """(embedding, final norm, lm_head or None when tied) as the checkpoint names them (text_model.rs:159-193)."""
+        if self.block_kind == "nigenex":
+            return "embed", "final.norm", "head"
+        p = self.model_prefix
+        return f"{p}.embed_tokens.weight", f"{p}.norm.weight", None if self.tie_word_embeddings else "lm_head.weight"
+
+    @property
     def hd(self) -> int:
         # attention.rs:85
         return self.head_dim if self.head_dim else self.hidden_size // self.num_attention_heads
@@ -101,6 +131,8 @@ class Config:
 
     def layer_name(self, i: int) -> str:
         # text_model.rs:205  "{prefix}.layers.{i}"
+        if self.block_kind == "nigenex":
+            return f"l{i}"
         return f"{self.model_prefix}.layers.{i}"
 
     # ---- HF config.json mappings -------------------------------------------------------------
@@ -132,7 +164,45 @@ class Config:
         return ""
 
     @staticmethod
+    def _from_nigenex(d: dict, max_seq: int = 4096) -> "Config":
+        """Nigenex ``config.json``: ``width``, ``vocab``, ``norm.eps``, ``logit_softcap`` and ``layers``, a list whose
+        entries give ``type`` (the mixer; only ``attention`` exists), the mixer's sizes and constants (``mixer``: heads,
+        kv_heads, dim, vdim, scale, softcap, mask.size) and the feed-forward (``mlp``: kind ``dense`` with ``ff``, or null).
+        Nothing is assumed equal between layers."""
+        specs = []
+        for i, L in enumerate(d["layers"]):
+            if L.get("type") != "attention":
+                raise ValueError(f"layer {i}: mixer type {L.get('type')!r} is not part of this design")
+            m = L["mixer"]
+            if int(m.get("vdim", m["dim"])) != int(m["dim"]):
+                raise ValueError(f"layer {i}: the values are the keys, so vdim {m['vdim']} must equal dim {m['dim']}")
+            mlp = L.get("mlp")
+            if mlp is not None and mlp.get("kind") != "dense":
+                raise ValueError(f"layer {i}: feed-forward kind {mlp.get('kind')!r} is not part of this design")
+            mask = m.get("mask") or {}
+            specs.append(LayerSpec(heads=int(m["heads"]), kv_heads=int(m["kv_heads"]), head_dim=int(m["dim"]),
+                                   window=int(mask.get("size") or 0), scale=float(m["scale"]), softcap=float(m.get("softcap") or 0.0),
+                                   ff=int(mlp["ff"]) if mlp is not None else 0, act=1))
+        if not specs:
+            raise ValueError("config lists no layers")
+        return Config(hidden_size=int(d["width"]), intermediate_size=max(s.ff for s in specs), vocab_size=int(d["vocab"]),
+                      num_hidden_layers=len(specs), num_attention_heads=specs[0].heads, num_key_value_heads=specs[0].kv_heads,
+                      rms_norm_eps=float(d["norm"]["eps"]), head_dim=specs[0].head_dim, max_seq_len=int(max_seq),
+                      block_kind="nigenex", layers=specs, logit_softcap=float(d.get("logit_softcap") or 0.0), model_prefix="")
+
+    def to_nigenex(self) -> dict:
+        """The ``config.json`` of a layer-list Config (inverse of ``_from_nigenex``)."""
+        return {"architecture": "Nigenex", "width": self.hidden_size, "vocab": self.vocab_size, "norm": {"eps": self.rms_norm_eps},
+                "logit_softcap": self.logit_softcap,
+                "layers": [{"type": "attention",
+                            "mixer": {"heads": s.heads, "kv_heads": s.kv_heads, "dim": s.head_dim, "vdim": s.head_dim, "scale": s.scale,
+                                      "softcap": s.softcap, "mask": {"size": s.window}},
+                            "mlp": {"kind": "dense", "ff": s.ff} if s.ff else None} for s in self.layers]}
+
+    @staticmethod
     def from_hf(d: dict) -> "Config":
+        if d.get("architecture") == "Nigenex":  # a single string, not HF's ``architectures`` list
+            return Config._from_nigenex(d)
         arch = Config.detect_arch(d)
         if arch in Config._OTHER_BLOCKS:
             raise ValueError(f"architecture {arch!r} is outside the block-forward path built here")
@@ -215,6 +285,8 @@ class Config:
             return Config.from_hf(json.load(f))
 
     def to_hf(self, arch: str = "LlamaForCausalLM") -> dict:
+        if self.block_kind == "nigenex":
+            return self.to_nigenex()
         d = dict(
             architectures=[arch], hidden_size=self.hidden_size, intermediate_size=self.intermediate_size,
             vocab_size=self.vocab_size, num_hidden_layers=self.num_hidden_layers,
@@ -260,6 +332,7 @@ class CConfig(ctypes.Structure):
         ("dtype", ctypes.c_int),
         ("sliding_window", ctypes.c_int), ("use_gelu_mlp", ctypes.c_int), ("embed_scale", ctypes.c_float),
         ("pre_reshape_qk_norm", ctypes.c_int),
+        ("layer_list", ctypes.c_int), ("logit_softcap", ctypes.c_float), ("scalar_final_norm", ctypes.c_int),
     ]
 
     @staticmethod
@@ -278,6 +351,7 @@ class CConfig(ctypes.Structure):
             rs.high_freq_factor if llama3 else 4.0, rs.original_max_position_embeddings if llama3 else 0,
             DTYPES[dtype],
             win, int(c.use_gelu_mlp), float(c.embed_scale or 0.0), int(c.pre_reshape_qk_norm),
+            int(c.layer_list), float(c.logit_softcap), int(c.layer_list),
         )
 
 

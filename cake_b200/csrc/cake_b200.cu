@@ -23,8 +23,10 @@
 #include "attn_decode.cuh"
 #include "attn_prefill.cuh"
 #include "attn_prefill_tc.cuh"
+#include "attn_window_bias.cuh"
 #include "common.cuh"
 #include "decode_mega.cuh"
+#include "f32_stream.cuh"
 #include "gemm_tc.cuh"
 #include "gemv.cuh"
 #include "prefill.cuh"
@@ -137,6 +139,11 @@ struct cake_b200_ctx {
   void *pf_h = nullptr, *pf_qkv = nullptr, *pf_y = nullptr, *pf_x1 = nullptr, *pf_gu = nullptr, *pf_mm = nullptr;
   void *io_x = nullptr;
   size_t io_x_cap = 0;
+  // layer-list blocks (fp32 residual stream): operands of the matrix products in D, sized on demand
+  size_t sp_rows = 0, sp_in_cols = 0, sp_out_cols = 0, sp_logit_rows = 0;
+  void *sp_h = nullptr, *sp_hs = nullptr, *sp_in = nullptr, *sp_a = nullptr, *sp_hn = nullptr;
+  float *sp_logits = nullptr;
+  int *sp_rows_idx = nullptr;
   // comm
   ncclComm_t comm = nullptr;
   int rank = 0, world = 1;
@@ -180,6 +187,13 @@ struct cake_b200_block {
   void *pan = nullptr, *pfn = nullptr;  // post-attention / post-feedforward RmsNorm vectors
   int window = -1;                      // -1: the config's
   bool use_rope = true;
+  // cake_b200_block_load_spec: a layer of a layer-list model (fp32 residual stream)
+  bool listed = false;
+  cake_b200_layer_spec spec{};
+  void *w_in = nullptr;    // rows = cat(q, k, gate), zero rows up to n_in_pad
+  void *w_out = nullptr;   // [hidden, heads*hd + ff] = o and down side by side along K
+  void *g = nullptr, *shift = nullptr, *r1 = nullptr, *r2 = nullptr;
+  int n_in = 0, n_in_pad = 0, gate_col = -1, k_out = 0;
   bool variant() const { return !ln1 || !ln2 || pan || pfn || window >= 0 || !use_rope || ctx->cfg.pre_reshape_qk_norm; }
 };
 
@@ -191,13 +205,23 @@ struct cake_b200_cache {
   std::vector<void *> k, v;
   std::vector<int> len;
   int *d_pos = nullptr;
+  // layer-list blocks: the row width the layer's K cache was allocated with, and the token-shift state (the last h of the
+  // previous call, fp32 [batch, hidden]) in two buffers that swap roles every call
+  std::vector<int> kv_heads, kv_hd;
+  std::vector<float *> shift_state[2];
+  std::vector<int> shift_cur;
 };
 
 template <typename U> struct TypeTag { typedef U type; };
 template <typename F> static inline int dispatch_T(int dtype, F &&f) {
-  if (dtype == CAKE_B200_BF16) return f(TypeTag<__nv_bfloat16>{});
+  if (dtype != CAKE_B200_F16) return f(TypeTag<__nv_bfloat16>{});  // an fp32 layer-list model hands its samplers bf16 logits
   return f(TypeTag<__half>{});
 }
+template <typename F> static inline int dispatch_T3(int dtype, F &&f) {
+  if (dtype == CAKE_B200_F32) return f(TypeTag<float>{});
+  return dispatch_T(dtype, f);
+}
+#define DISPATCH_T3(dtype, ...) dispatch_T3((dtype), __VA_ARGS__)
 // usage: DISPATCH_T(dtype, [&](auto tag_) -> int { typedef typename decltype(tag_)::type T; ... })
 #define DISPATCH_T(dtype, ...) dispatch_T((dtype), __VA_ARGS__)
 #define T_LAMBDA [&](auto tag_) -> int
@@ -377,8 +401,20 @@ static void f32_to_D(const std::vector<float> &src, std::vector<uint16_t> &dst, 
 
 extern "C" int cake_b200_ctx_create(int device, const cake_b200_config *cfg, cake_b200_ctx **out) {
   if (!cfg || !out) return fail(CAKE_B200_EINVAL, "null argument");
+  cake_b200_config listed_cfg;
+  if (cfg->layer_list) {
+    // every per-layer size comes with the layers; the fields the Llama-family paths size their workspaces by are set to the
+    // smallest legal values so that those workspaces exist (samplers, token staging) but cost nothing
+    if (cfg->dtype != CAKE_B200_BF16 && cfg->dtype != CAKE_B200_F16 && cfg->dtype != CAKE_B200_F32)
+      return fail(CAKE_B200_EINVAL, "dtype %d unsupported (bf16=0, f16=1, f32=2)", cfg->dtype);
+    if (cfg->hidden < 1 || cfg->n_layers < 1 || cfg->vocab < 1 || cfg->max_seq < 1) return fail(CAKE_B200_EINVAL, "config dimensions must be positive");
+    listed_cfg = *cfg;
+    listed_cfg.inter = 64; listed_cfg.n_heads = 1; listed_cfg.n_kv_heads = 1; listed_cfg.head_dim = 16;
+    listed_cfg.partial_rotary = 0.f; listed_cfg.rope_llama3 = 0; listed_cfg.sliding_window = 0;
+    cfg = &listed_cfg;
+  } else {
   if (cfg->dtype != CAKE_B200_BF16 && cfg->dtype != CAKE_B200_F16)
-    return fail(CAKE_B200_EINVAL, "dtype %d unsupported (bf16=0, f16=1)", cfg->dtype);
+    return fail(CAKE_B200_EINVAL, "dtype %d unsupported (bf16=0, f16=1; f32 is for layer-list models)", cfg->dtype);
   if (cfg->hidden < 1 || cfg->inter < 1 || cfg->n_heads < 1 || cfg->n_kv_heads < 1 || cfg->n_layers < 1 || cfg->vocab < 1 || cfg->max_seq < 1)
     return fail(CAKE_B200_EINVAL, "config dimensions must be positive");
   if (cfg->n_heads % cfg->n_kv_heads != 0 || cfg->n_heads / cfg->n_kv_heads > ATTN_MAX_G)
@@ -387,6 +423,7 @@ extern "C" int cake_b200_ctx_create(int device, const cake_b200_config *cfg, cak
     return fail(CAKE_B200_EINVAL, "head_dim %d unsupported (16/32/64/128/256)", cfg->head_dim);
   if (cfg->hidden % 64 || cfg->inter % 64 || (cfg->n_heads * cfg->head_dim) % 64)
     return fail(CAKE_B200_EINVAL, "hidden, intermediate and n_heads*head_dim must be multiples of 64");
+  }
   int ndev = 0;
   CU(cudaGetDeviceCount(&ndev));
   if (ndev == 0) return fail(CAKE_B200_ECUDA, "no CUDA device: libcake_b200 has no CPU fallback");
@@ -399,7 +436,7 @@ extern "C" int cake_b200_ctx_create(int device, const cake_b200_config *cfg, cak
   struct Guard { cake_b200_ctx *c; ~Guard() { if (c) { cake_b200_ctx_destroy(c); (void)cudaGetLastError(); } } } guard{c};
   c->device = device;
   c->cfg = *cfg;
-  c->es = 2;
+  c->es = cfg->dtype == CAKE_B200_F32 ? 4 : 2;
   c->sm_count = prop.multiProcessorCount;
   c->rot = (int)((float)cfg->head_dim * cfg->partial_rotary);
   c->nqkv = (cfg->n_heads + 2 * cfg->n_kv_heads) * cfg->head_dim;
@@ -410,8 +447,8 @@ extern "C" int cake_b200_ctx_create(int device, const cake_b200_config *cfg, cak
   std::vector<float> cs, sn;
   rope_tables_host(*cfg, cs, sn, c->rot);
   std::vector<uint16_t> cd, sd;
-  f32_to_D(cs, cd, cfg->dtype);
-  f32_to_D(sn, sd, cfg->dtype);
+  f32_to_D(cs, cd, cfg->dtype == CAKE_B200_F16 ? CAKE_B200_F16 : CAKE_B200_BF16);
+  f32_to_D(sn, sd, cfg->dtype == CAKE_B200_F16 ? CAKE_B200_F16 : CAKE_B200_BF16);
   const size_t tb = cd.size() * 2 + 16;
   CU(cudaMalloc(&c->cos_t, tb));
   CU(cudaMalloc(&c->sin_t, tb));
@@ -486,7 +523,7 @@ extern "C" void cake_b200_ctx_destroy(cake_b200_ctx *c) {
                   c->ws_acc, c->part_val, c->part_idx, c->d_step, c->attn_counters, c->argmax_counter, c->d_token,
                   c->token_ring, c->d_ids, c->d_pen, c->pf_h, c->pf_qkv, c->pf_y, c->pf_x1, c->pf_gu, c->pf_mm, c->io_x,
                   c->gbar, c->mk_tab_dev, c->g_tab_dev, c->tickets, c->ring_seq, c->inbox, c->step_trace, c->trace,
-                  c->samp_p, c->samp_noise, c->x0};
+                  c->samp_p, c->samp_noise, c->x0, c->sp_h, c->sp_hs, c->sp_in, c->sp_a, c->sp_hn, c->sp_logits, c->sp_rows_idx};
   for (void *b : bufs)
     if (b) cudaFree(b);
   if (c->lm_head && c->lm_head != c->embed) cudaFree(c->lm_head);
@@ -670,7 +707,8 @@ extern "C" int cake_b200_block_load(cake_b200_ctx *c, int layer_idx, const void 
 extern "C" void cake_b200_block_free(cake_b200_block *b) {
   if (!b) return;
   cudaSetDevice(b->device);
-  void *bufs[] = {b->wqkv, b->wo, b->wgu, b->wd, b->ln1, b->ln2, b->bqkv, b->qn, b->kn, b->pan, b->pfn};
+  void *bufs[] = {b->wqkv, b->wo, b->wgu, b->wd, b->ln1, b->ln2, b->bqkv, b->qn, b->kn, b->pan, b->pfn,
+                  b->w_in, b->w_out, b->g, b->shift, b->r1, b->r2};
   for (void *p : bufs)
     if (p) cudaFree(p);  // cudaFree synchronises with outstanding work
   (void)cudaGetLastError();
@@ -706,6 +744,11 @@ extern "C" int cake_b200_cache_create(cake_b200_ctx *c, int batch, int max_seq, 
   k->k.assign(c->cfg.n_layers, nullptr);
   k->v.assign(c->cfg.n_layers, nullptr);
   k->len.assign(c->cfg.n_layers, 0);
+  k->kv_heads.assign(c->cfg.n_layers, 0);
+  k->kv_hd.assign(c->cfg.n_layers, 0);
+  k->shift_state[0].assign(c->cfg.n_layers, nullptr);
+  k->shift_state[1].assign(c->cfg.n_layers, nullptr);
+  k->shift_cur.assign(c->cfg.n_layers, 0);
   cudaError_t e = cudaMalloc(&k->d_pos, 4);
   if (e == cudaSuccess) e = cudaMemset(k->d_pos, 0, 4);
   if (e != cudaSuccess) {
@@ -751,6 +794,9 @@ extern "C" void cake_b200_cache_free(cake_b200_cache *k) {
     if (p) cudaFree(p);
   for (void *p : k->v)
     if (p) cudaFree(p);
+  for (auto &v : k->shift_state)
+    for (float *p : v)
+      if (p) cudaFree(p);
   cudaFree(k->d_pos);
   (void)cudaGetLastError();
   delete k;
@@ -764,7 +810,9 @@ extern "C" int cake_b200_cache_read(cake_b200_cache *k, int block_idx, int which
   cake_b200_ctx *c = k->ctx;
   CU(cudaSetDevice(c->device));
   if (block_idx < 0 || block_idx >= (int)k->len.size() || !k->k[block_idx]) return fail(CAKE_B200_EINVAL, "layer %d has no cache", block_idx);
-  const int len = k->len[block_idx], hd = c->cfg.head_dim, nkv = c->cfg.n_kv_heads;
+  const int len = k->len[block_idx];
+  const int hd = k->kv_hd[block_idx] ? k->kv_hd[block_idx] : c->cfg.head_dim, nkv = k->kv_heads[block_idx] ? k->kv_heads[block_idx] : c->cfg.n_kv_heads;
+  if (which && !k->v[block_idx]) return fail(CAKE_B200_EINVAL, "layer %d keeps no V cache (its values are its keys)", block_idx);
   const size_t need = (size_t)k->batch * nkv * len * hd * c->es;
   if (bytes < need) return fail(CAKE_B200_EINVAL, "cache_read needs %zu bytes", need);
   CU(cudaStreamSynchronize(c->stream));
@@ -779,6 +827,7 @@ extern "C" int cake_b200_cache_fill_synthetic(cake_b200_cache *k, const int *blo
   cake_b200_ctx *c = k->ctx;
   CU(cudaSetDevice(c->device));
   if (len > k->cap) return fail(CAKE_B200_EINVAL, "len %d > cache capacity %d", len, k->cap);
+  if (c->cfg.layer_list) return fail(CAKE_B200_EINVAL, "cache_fill_synthetic is for the Llama-family blocks");
   for (int i = 0; i < n_blocks; i++) {
     const int l = block_idx[i];
     RC(cache_ensure(k, l));
@@ -1247,6 +1296,152 @@ static int enqueue_prefill_layers(cake_b200_ctx *c, cake_b200_block *const *bloc
   });
 }
 
+
+// ------------------------------------------------------------------------------------------ layer-list blocks (fp32 residual stream)
+// include/cake_b200.h, cake_b200_layer_spec: parallel block, scalar/vector RMS norm in fp32, token shift, attention with
+// soft cap / distance bias / window / keys as values / head gate (attn_window_bias.cuh), gated feed-forward.
+static int round_up(int v, int m) { return (v + m - 1) / m * m; }
+
+extern "C" int cake_b200_block_load_spec(cake_b200_ctx *c, int layer_idx, const cake_b200_layer_spec *sp,
+                                         const cake_b200_layer_tensors *t, cake_b200_block **out) {
+  if (!c || !sp || !t || !out) return fail(CAKE_B200_EINVAL, "null argument");
+  if (!c->cfg.layer_list) return fail(CAKE_B200_EINVAL, "block_load_spec needs a ctx created with layer_list = 1");
+  if (sp->heads < 1 || sp->kv_heads < 1 || sp->heads % sp->kv_heads || sp->head_dim < 1 || sp->head_dim > WA_MAX_HD)
+    return fail(CAKE_B200_EINVAL, "layer %d: heads %d / kv_heads %d / head_dim %d unsupported (heads a multiple of kv_heads, head_dim <= %d)",
+                layer_idx, sp->heads, sp->kv_heads, sp->head_dim, WA_MAX_HD);
+  if (!sp->values_are_keys || t->v) return fail(CAKE_B200_EINVAL, "layer %d: a separate value projection is not built for layer-list blocks", layer_idx);
+  if (sp->window < 0 || sp->ff < 0 || !(sp->scale > 0.f) || sp->softcap < 0.f) return fail(CAKE_B200_EINVAL, "layer %d: bad window / ff / scale / softcap", layer_idx);
+  if (!t->norm || !t->q || !t->k || !t->o || (!t->r1) != (!t->r2)) return fail(CAKE_B200_EINVAL, "layer %d: null weight pointer", layer_idx);
+  if (sp->ff > 0 && (!t->ff_gate || !t->ff_up || !t->ff_down)) return fail(CAKE_B200_EINVAL, "layer %d: ff = %d but a feed-forward pointer is null", layer_idx, sp->ff);
+  CU(cudaSetDevice(c->device));
+  const size_t es = c->es, H = c->cfg.hidden, hd = sp->head_dim, sq = (size_t)sp->heads * hd, skv = (size_t)sp->kv_heads * hd, I = sp->ff;
+  auto *b = new cake_b200_block{c, layer_idx, c->device};
+  b->listed = true;
+  b->spec = *sp;
+  const int rc = [&]() -> int {
+    // one input projection: rows cat(q, k, gate); padded with zero rows to the tensor-core tile so that it can take the shape
+    b->n_in = (int)(sq + skv + (t->gate ? sp->heads : 0));
+    b->n_in_pad = round_up(b->n_in, TC_BN);
+    b->gate_col = t->gate ? (int)(sq + skv) : -1;
+    CU(cudaMalloc(&b->w_in, (size_t)b->n_in_pad * H * es + 16));
+    CU(cudaMemsetAsync(b->w_in, 0, (size_t)b->n_in_pad * H * es, 0));
+    CU(cudaStreamSynchronize(0));
+    RC(pipe_copy(c, b->w_in, sq * H * es, t->q, sq * H * es, sq * H * es, 1));
+    RC(pipe_copy(c, (char *)b->w_in + sq * H * es, skv * H * es, t->k, skv * H * es, skv * H * es, 1));
+    if (t->gate) RC(pipe_copy(c, (char *)b->w_in + (sq + skv) * H * es, sp->heads * H * es, t->gate, sp->heads * H * es, sp->heads * H * es, 1));
+    // one output projection over K = heads*hd + ff: row n = [o[n, :], down[n, :]] — mixer and feed-forward of a parallel
+    // block add into the same residual, so they are one matrix product over the concatenated activations
+    b->k_out = (int)(sq + I);
+    CU(cudaMalloc(&b->w_out, H * (sq + I) * es + 16));
+    RC(pipe_copy(c, b->w_out, (sq + I) * es, t->o, sq * es, sq * es, H));
+    if (I) {
+      RC(pipe_copy(c, (char *)b->w_out + sq * es, (sq + I) * es, t->ff_down, I * es, I * es, H));
+      CU(cudaMalloc(&b->wgu, 2 * I * H * es + 16));  // row-interleaved gate / up, as cake_b200_block_load lays them out
+      RC(pipe_copy(c, b->wgu, 2 * H * es, t->ff_gate, H * es, H * es, I));
+      RC(pipe_copy(c, (char *)b->wgu + H * es, 2 * H * es, t->ff_up, H * es, H * es, I));
+    }
+    RC(upload(c, &b->g, t->norm, (sp->scalar_norm ? 1 : H) * es));
+    if (t->shift) RC(upload(c, &b->shift, t->shift, H * es));
+    if (t->r1) {
+      RC(upload(c, &b->r1, t->r1, sp->heads * es));
+      RC(upload(c, &b->r2, t->r2, sp->heads * es));
+    }
+    return pipe_mark(c);
+  }();
+  if (rc != CAKE_B200_OK) {
+    cake_b200_block_free(b);
+    return rc;
+  }
+  *out = b;
+  return CAKE_B200_OK;
+}
+
+static int cache_ensure_listed(cake_b200_cache *k, int layer, const cake_b200_block *b) {
+  if (layer < 0 || layer >= (int)k->k.size()) return fail(CAKE_B200_EINVAL, "block_idx %d out of range", layer);
+  cake_b200_ctx *c = k->ctx;
+  const int nkv = b->spec.kv_heads, hd = b->spec.head_dim;
+  if (k->k[layer] && (k->kv_heads[layer] != nkv || k->kv_hd[layer] != hd))
+    return fail(CAKE_B200_ESTATE, "block_idx %d was used with another layer geometry in this cache", layer);
+  if (!k->k[layer]) {
+    CU(cudaMalloc(&k->k[layer], (size_t)k->batch * nkv * k->cap * hd * c->es + 16));  // values are the keys: no V buffer
+    k->kv_heads[layer] = nkv;
+    k->kv_hd[layer] = hd;
+  }
+  if (b->shift && !k->shift_state[0][layer])
+    for (int i = 0; i < 2; i++) CU(cudaMalloc(&k->shift_state[i][layer], (size_t)k->batch * c->cfg.hidden * sizeof(float)));
+  return CAKE_B200_OK;
+}
+
+static int sp_reserve(cake_b200_ctx *c, size_t rows, size_t in_cols, size_t out_cols) {
+  if (rows <= c->sp_rows && in_cols <= c->sp_in_cols && out_cols <= c->sp_out_cols) return CAKE_B200_OK;
+  CU(cudaStreamSynchronize(c->stream));
+  rows = std::max(rows, c->sp_rows); in_cols = std::max(in_cols, c->sp_in_cols); out_cols = std::max(out_cols, c->sp_out_cols);
+  void **bufs[] = {&c->sp_h, &c->sp_hs, &c->sp_in, &c->sp_a};
+  for (void **b : bufs)
+    if (*b) { cudaFree(*b); *b = nullptr; }
+  c->sp_rows = c->sp_in_cols = c->sp_out_cols = 0;
+  const size_t es = c->es, H = c->cfg.hidden;
+  CU(cudaMalloc(&c->sp_h, rows * H * es + 16));
+  CU(cudaMalloc(&c->sp_hs, rows * H * es + 16));
+  CU(cudaMalloc(&c->sp_in, rows * in_cols * es + 16));
+  CU(cudaMalloc(&c->sp_a, rows * out_cols * es + 16));
+  c->sp_rows = rows; c->sp_in_cols = in_cols; c->sp_out_cols = out_cols;
+  return CAKE_B200_OK;
+}
+
+template <typename T, int EPI> static int gemm_rows_T(cake_b200_ctx *c, const RowsGemm &g) {
+  dim3 grid((g.N + RG_BN - 1) / RG_BN, (g.M + RG_BM - 1) / RG_BM), block(256);
+  return launch_pdl(c, gemm_rows_kernel<T, EPI>, grid, block, 0, g);
+}
+
+// x_in, x_out: [B, S, hidden] fp32 (may alias).  Per layer: norm+shift -> input projection -> K append -> attention ->
+// gate/up with the activation -> output projection over [attention | feed-forward] with the fp32 residual add.
+static int enqueue_listed_layers(cake_b200_ctx *c, cake_b200_block *const *blocks, const int *block_idx, int n,
+                                 cake_b200_cache *kc, const float *x_in, float *x_out, int B, int S, int pos0) {
+  const int H = c->cfg.hidden, M = B * S;
+  size_t in_cols = 0, out_cols = 0;
+  for (int i = 0; i < n; i++) {
+    in_cols = std::max(in_cols, (size_t)blocks[i]->n_in_pad);
+    out_cols = std::max(out_cols, (size_t)blocks[i]->k_out);
+  }
+  RC(sp_reserve(c, (size_t)M, in_cols, out_cols));
+  return DISPATCH_T3(c->cfg.dtype, T_LAMBDA {
+    typedef typename decltype(tag_)::type T;
+    const float *cur = x_in;
+    for (int i = 0; i < n; i++) {
+      const cake_b200_block *b = blocks[i];
+      const cake_b200_layer_spec &sp = b->spec;
+      const int l = block_idx[i], hd = sp.head_dim, sq = sp.heads * hd;
+      // 1. h = norm(x) (for the feed-forward) and its token-shifted copy (for the mixer)
+      const int cs = kc->shift_cur[l];
+      const T *mix_in = (const T *)(b->shift ? c->sp_hs : c->sp_h);
+      RC(launch_pdl(c, norm_shift_rows_kernel<T>, dim3(M), dim3(256), 0, cur, (const int *)nullptr, (const T *)b->g, sp.scalar_norm ? 0 : 1,
+                    (const T *)b->shift, (const float *)kc->shift_state[cs][l], kc->shift_state[cs ^ 1][l], (T *)c->sp_h, (T *)c->sp_hs, S, H,
+                    c->cfg.rms_eps, pos0));
+      // 2. q | k | gate logits in one product
+      RowsGemm gi{mix_in, b->w_in, nullptr, c->sp_in, M, b->n_in, H, H, b->n_in_pad, 0, 0.f};
+      RC((gemm_rows_T<T, RE_STORE>(c, gi)));
+      // 3. the step's keys join the cache, then attention reads keys (= values) only from there
+      RC(launch_pdl(c, rows_to_cache_kernel<T>, dim3(M), dim3(128), 0, (const T *)c->sp_in, (T *)kc->k[l], S, b->n_in_pad, sq, sp.kv_heads, hd,
+                    kc->cap, pos0));
+      WinAttn wa{c->sp_in, kc->k[l], kc->k[l], b->r1, b->r2, c->sp_a, B, S, sp.heads, sp.kv_heads, hd, kc->cap, pos0, b->n_in_pad, b->k_out,
+                 b->gate_col, sp.window, sp.scale, sp.softcap};
+      const long items = (long)M * sp.heads;
+      RC(launch_pdl(c, attn_window_bias_kernel<T>, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, wa));
+      // 4. feed-forward input half: act(gate h) * (up h), written next to the attention output
+      if (sp.ff > 0) {
+        RowsGemm gu{c->sp_h, b->wgu, nullptr, (T *)c->sp_a + sq, M, 2 * sp.ff, H, H, b->k_out, sp.act, 0.f};
+        RC((gemm_rows_T<T, RE_GATE_UP>(c, gu)));
+      }
+      // 5. x <- x + [attention | ff] . [o | down]^T
+      RowsGemm go{c->sp_a, b->w_out, cur, x_out, M, H, b->k_out, b->k_out, H, 0, 0.f};
+      RC((gemm_rows_T<T, RE_RESIDUAL_F32>(c, go)));
+      cur = x_out;
+    }
+    return CAKE_B200_OK;
+  });
+}
+
 // ------------------------------------------------------------------------------------------ forward_batch
 extern "C" int cake_b200_forward_batch(cake_b200_ctx *c, cake_b200_block *const *blocks, const int *block_idx,
                                        int n_blocks, cake_b200_cache *kc, const void *x_dev, void *y_dev, int batch,
@@ -1257,11 +1452,27 @@ extern "C" int cake_b200_forward_batch(cake_b200_ctx *c, cake_b200_block *const 
     return fail(CAKE_B200_ESTATE, "index_pos %d + seq %d exceeds cache capacity %d", index_pos, seq, kc->cap);
   CU(cudaSetDevice(c->device));
   RC(wait_loads(c));
+  bool listed = false;
   for (int i = 0; i < n_blocks; i++) {
-    RC(cache_ensure(kc, block_idx[i]));
+    if (!blocks[i]) return fail(CAKE_B200_EINVAL, "blocks[%d] is null", i);
+    listed = listed || blocks[i]->listed;
+    if (blocks[i]->listed != listed) return fail(CAKE_B200_EINVAL, "layer-list blocks and Llama-family blocks cannot share a call");
+  }
+  for (int i = 0; i < n_blocks; i++) {
+    if (listed) RC(cache_ensure_listed(kc, block_idx[i], blocks[i]));
+    else RC(cache_ensure(kc, block_idx[i]));
     if (kc->len[block_idx[i]] != index_pos)
       return fail(CAKE_B200_ESTATE, "block %d: index_pos %d != cache length %d (clear the cache or feed positions in order)",
                   block_idx[i], index_pos, kc->len[block_idx[i]]);
+  }
+  if (listed) {  // fp32 residual stream: x_dev / y_dev are float
+    RC(enqueue_listed_layers(c, blocks, block_idx, n_blocks, kc, (const float *)x_dev, (float *)y_dev, batch, seq, index_pos));
+    for (int i = 0; i < n_blocks; i++) {
+      kc->len[block_idx[i]] = index_pos + seq;
+      if (blocks[i]->shift) kc->shift_cur[block_idx[i]] ^= 1;
+    }
+    CU(cudaGetLastError());
+    return CAKE_B200_OK;
   }
   bool variant = false;  // sibling block structures step through the batched path (cake_b200_block_set_variant)
   for (int i = 0; i < n_blocks; i++) {
@@ -1305,7 +1516,7 @@ extern "C" int cake_b200_forward_batch_host(cake_b200_ctx *c, cake_b200_block *c
   if (index_pos < 0 || (long long)index_pos + (long long)seq > (long long)kc->cap)
     return fail(CAKE_B200_ESTATE, "index_pos %d + seq %d exceeds cache capacity %d", index_pos, seq, kc->cap);
   CU(cudaSetDevice(c->device));
-  const size_t bytes = (size_t)batch * seq * c->cfg.hidden * c->es;
+  const size_t bytes = (size_t)batch * seq * c->cfg.hidden * (c->cfg.layer_list ? sizeof(float) : c->es);
   RC(io_reserve(c, bytes));
   memcpy(c->h_pin_x, x_host, bytes);
   CU(cudaMemcpyAsync(c->io_x, c->h_pin_x, bytes, cudaMemcpyHostToDevice, c->stream));
@@ -1323,7 +1534,7 @@ extern "C" int cake_b200_head_load(cake_b200_ctx *c, const void *embed, const vo
   CU(cudaSetDevice(c->device));
   const size_t es = c->es, H = c->cfg.hidden, V = c->cfg.vocab;
   RC(upload(c, &c->embed, embed, V * H * es));
-  RC(upload(c, &c->ln_f, ln_f, H * es));
+  RC(upload(c, &c->ln_f, ln_f, (c->cfg.layer_list && c->cfg.scalar_final_norm ? 1 : H) * es));
   if (lm_head) RC(upload(c, &c->lm_head, lm_head, V * H * es));
   else c->lm_head = c->embed;  // text_model.rs:164-167
   return pipe_mark(c);
@@ -1346,6 +1557,12 @@ extern "C" int cake_b200_embed(cake_b200_ctx *c, const uint32_t *ids_host, int b
   }
   CU(cudaMemcpyAsync(c->d_ids, ids_host, n * 4, cudaMemcpyHostToDevice, c->stream));
   // the ids buffer is pageable in general: the copy above returns after staging, safe to reuse
+  if (c->cfg.layer_list)  // the fp32 residual stream starts here
+    return DISPATCH_T3(c->cfg.dtype, T_LAMBDA {
+      typedef typename decltype(tag_)::type T;
+      return launch_pdl(c, embed_f32_kernel<T>, dim3((unsigned)n), dim3(128), 0, (const T *)c->embed, (const uint32_t *)c->d_ids,
+                        (float *)x_dev, (int)n, c->cfg.hidden, c->cfg.vocab, c->cfg.embed_scale);
+    });
   RC(DISPATCH_T(c->cfg.dtype, T_LAMBDA {
       typedef typename decltype(tag_)::type T;
     return launch_pdl(c, embed_kernel<T>, dim3((unsigned)n), dim3(128), 0, (const T *)c->embed, (const uint32_t *)c->d_ids,
@@ -1354,12 +1571,76 @@ extern "C" int cake_b200_embed(cake_b200_ctx *c, const uint32_t *ids_host, int b
   return CAKE_B200_OK;
 }
 
+
+// fp32 logits of n rows of the fp32 stream: final norm (scalar or vector gain) -> lm_head -> soft cap
+static int listed_logits(cake_b200_ctx *c, const void *x_dev, const int *rows_host, int n, float *out_dev) {
+  const size_t H = c->cfg.hidden, V = c->cfg.vocab;
+  if ((size_t)n > c->sp_logit_rows) {
+    CU(cudaStreamSynchronize(c->stream));
+    if (c->sp_hn) cudaFree(c->sp_hn);
+    if (c->sp_rows_idx) cudaFree(c->sp_rows_idx);
+    if (c->sp_logits) cudaFree(c->sp_logits);
+    c->sp_hn = nullptr; c->sp_rows_idx = nullptr; c->sp_logits = nullptr; c->sp_logit_rows = 0;
+    CU(cudaMalloc(&c->sp_hn, (size_t)n * H * c->es + 16));
+    CU(cudaMalloc(&c->sp_rows_idx, (size_t)n * sizeof(int)));
+    CU(cudaMalloc(&c->sp_logits, (size_t)n * V * sizeof(float)));
+    c->sp_logit_rows = n;
+  }
+  CU(cudaMemcpyAsync(c->sp_rows_idx, rows_host, (size_t)n * sizeof(int), cudaMemcpyHostToDevice, c->stream));
+  CU(cudaStreamSynchronize(c->stream));  // rows_host is the caller's (pageable) memory
+  return DISPATCH_T3(c->cfg.dtype, T_LAMBDA {
+    typedef typename decltype(tag_)::type T;
+    RC(launch_pdl(c, norm_shift_rows_kernel<T>, dim3(n), dim3(256), 0, (const float *)x_dev, (const int *)c->sp_rows_idx, (const T *)c->ln_f,
+                  c->cfg.scalar_final_norm ? 0 : 1, (const T *)nullptr, (const float *)nullptr, (float *)nullptr, (T *)c->sp_hn, (T *)nullptr, 1,
+                  (int)H, c->cfg.rms_eps, 0));
+    RowsGemm g{c->sp_hn, c->lm_head, nullptr, out_dev ? out_dev : c->sp_logits, n, (int)V, (int)H, (int)H, (int)V, 0, c->cfg.logit_softcap};
+    return gemm_rows_T<T, RE_SOFTCAP_F32>(c, g);
+  });
+}
+// cake_b200_logits for a layer-list model: the last position of every batch row; logits_dev receives them in the 16-bit
+// dtype the samplers read (bf16 when D is fp32)
+static int listed_logits_last(cake_b200_ctx *c, const void *x_dev, int batch, int seq, void *logits_dev, uint32_t *argmax_host) {
+  std::vector<int> rows(batch);
+  for (int b = 0; b < batch; b++) rows[b] = b * seq + seq - 1;
+  RC(listed_logits(c, x_dev, rows.data(), batch, nullptr));
+  const size_t V = c->cfg.vocab;
+  if (!logits_dev && !argmax_host) return CAKE_B200_OK;
+  return DISPATCH_T(c->cfg.dtype, T_LAMBDA {
+    typedef typename decltype(tag_)::type T;
+    if (logits_dev) RC(launch_pdl(c, f32_to_T_kernel<T>, dim3(64), dim3(256), 0, (const float *)c->sp_logits, (T *)logits_dev, (size_t)batch * V));
+    if (argmax_host) {
+      for (int b = 0; b < batch; b++) {
+        T *row = logits_dev ? (T *)logits_dev + (size_t)b * V : (T *)c->logits;
+        if (!logits_dev) RC(launch_pdl(c, f32_to_T_kernel<T>, dim3(64), dim3(256), 0, (const float *)c->sp_logits + (size_t)b * V, row, V));
+        argmax_kernel<T><<<1, 1024, 0, c->stream>>>(row, (int)V, c->d_token);
+        c->launches++;
+        CU(cudaMemcpyAsync(c->h_pin + b, c->d_token, 4, cudaMemcpyDeviceToHost, c->stream));
+      }
+      CU(cudaStreamSynchronize(c->stream));
+      for (int b = 0; b < batch; b++) argmax_host[b] = c->h_pin[b];
+    }
+    return CAKE_B200_OK;
+  });
+}
+extern "C" int cake_b200_logits_rows(cake_b200_ctx *c, const void *x_dev, int n_rows_total, const int *rows_host, int n,
+                                     float *logits_f32_dev) {
+  if (!c || !x_dev || !rows_host || !logits_f32_dev || !c->lm_head) return fail(CAKE_B200_EINVAL, "null argument or head not loaded");
+  if (!c->cfg.layer_list) return fail(CAKE_B200_EINVAL, "logits_rows is for layer-list models (fp32 residual stream)");
+  if (n < 1) return fail(CAKE_B200_EINVAL, "logits_rows: n must be >= 1");
+  for (int i = 0; i < n; i++)
+    if (rows_host[i] < 0 || rows_host[i] >= n_rows_total) return fail(CAKE_B200_EINVAL, "row %d out of range (%d rows)", rows_host[i], n_rows_total);
+  CU(cudaSetDevice(c->device));
+  RC(wait_loads(c));
+  return listed_logits(c, x_dev, rows_host, n, logits_f32_dev);
+}
+
 extern "C" int cake_b200_logits(cake_b200_ctx *c, const void *x_dev, int batch, int seq, void *logits_dev,
                                 uint32_t *argmax_host) {
   if (!c || !x_dev || !c->lm_head) return fail(CAKE_B200_EINVAL, "null argument or head not loaded");
   if (batch > 64) return fail(CAKE_B200_EINVAL, "batch > 64");
   CU(cudaSetDevice(c->device));
   RC(wait_loads(c));
+  if (c->cfg.layer_list) return listed_logits_last(c, x_dev, batch, seq, logits_dev, argmax_host);
   const size_t H = c->cfg.hidden, V = c->cfg.vocab, es = c->es;
   for (int b = 0; b < batch; b++) {
     const char *row = (const char *)x_dev + ((size_t)b * seq + (seq - 1)) * H * es;  // text_model.rs:342-346

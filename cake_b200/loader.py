@@ -275,6 +275,33 @@ def block_tensors(vb, cfg: Config, name: str) -> Dict[str, Optional[torch.Tensor
     return out
 
 
+# argument order of ``cake_b200_layer_tensors`` (include/cake_b200.h) -> tensor name under the layer of a Nigenex checkpoint
+LISTED_TENSORS = (("norm", "norm1"), ("shift", "shift"), ("q", "mix.q"), ("k", "mix.k"), ("v", None), ("o", "mix.o"),
+                  ("r1", "mix.r1"), ("r2", "mix.r2"), ("gate", "mix.g"), ("ff_gate", "mlp.gate"), ("ff_up", "mlp.up"),
+                  ("ff_down", "mlp.down"))
+
+
+def listed_block_tensors(vb, cfg: Config, index: int) -> Dict[str, Optional[torch.Tensor]]:
+    """The tensors of layer ``index`` of a layer-list (Nigenex) checkpoint by the field names of ``cake_b200_layer_tensors``,
+    each checked against the shape its LayerSpec declares.  Linear weights are [out, in]; the norm gain is a single number."""
+    sp, H, name = cfg.layers[index], cfg.hidden_size, cfg.layer_name(index)
+    sq, skv = sp.heads * sp.head_dim, sp.kv_heads * sp.head_dim
+    shapes = {"norm": (), "shift": (H,), "q": (sq, H), "k": (skv, H), "o": (H, sq), "r1": (sp.heads,), "r2": (sp.heads,),
+              "gate": (sp.heads, H), "ff_gate": (sp.ff, H), "ff_up": (sp.ff, H), "ff_down": (H, sp.ff)}
+    out: Dict[str, Optional[torch.Tensor]] = {}
+    for fld, short in LISTED_TENSORS:
+        if short is None or (fld.startswith("ff_") and not sp.ff):
+            out[fld] = None
+            continue
+        t = vb.get(f"{name}.{short}")
+        if t is None:
+            raise KeyError(f"tensor {name}.{short} not found")
+        if tuple(t.shape) != tuple(shapes[fld]):
+            raise ValueError(f"shape mismatch for {name}.{short}, expected: {list(shapes[fld])}, got: {list(t.shape)}")
+        out[fld] = t
+    return out
+
+
 def detect_model_prefix(index_path: str, configured: str) -> str:
     """cake/mod.rs:335-357: the text before the first ``.layers.0.`` key of the index wins over the configured prefix."""
     if not os.path.exists(index_path):
@@ -329,7 +356,7 @@ def save_checkpoint(path: str, cfg: Config, tensors: Dict[str, torch.Tensor], ar
     order, a new shard starts when the current one would exceed ``shard_bytes``."""
     os.makedirs(path, exist_ok=True)
     with open(os.path.join(path, "config.json"), "w") as f:
-        json.dump(cfg.to_hf(arch), f)
+        json.dump(cfg.to_hf(arch), f)  # a layer-list Config writes its own format whatever ``arch`` says
     rev = {v: k for k, v in _DTYPES.items()}
     groups: List[List[str]] = [[]]
     used = 0

@@ -60,10 +60,16 @@ class Cache:
         return lib().cake_b200_cache_len(self.h, block_idx)
 
     def kv(self, block_idx: int) -> Tuple[torch.Tensor, torch.Tensor]:
-        """(K, V) copies of shape (batch, n_kv, len, hd) on the host, dtype D."""
+        """(K, V) copies of shape (batch, n_kv, len, hd) on the host, dtype D (a layer whose values are its keys returns
+        the same tensor twice: it keeps no V cache)."""
         c = self.ctx.config
         n = self.len(block_idx)
         out = []
+        if c.layer_list:
+            sp = c.layers[block_idx]
+            t = torch.empty((self.batch, sp.kv_heads, n, sp.head_dim), dtype=TORCH_DTYPES[self.ctx.dtype])
+            check(lib().cake_b200_cache_read(self.h, block_idx, 0, ptr(t), t.numel() * t.element_size()))
+            return t, t
         for which in (0, 1):
             t = torch.empty((self.batch, c.num_key_value_heads, n, c.hd), dtype=TORCH_DTYPES[self.ctx.dtype])
             check(lib().cake_b200_cache_read(self.h, block_idx, which, ptr(t), t.numel() * t.element_size()))
@@ -97,6 +103,9 @@ class Context:
         check(lib().cake_b200_ctx_create(device, byref(self.ccfg), byref(self.h)))
         self.cache: Optional[Cache] = Cache(self)
         self.torch_dtype = TORCH_DTYPES[dtype]
+        # layer-list models keep the residual stream in fp32 and hand their samplers 16-bit logits (bf16 when D is fp32)
+        self.stream_dtype = torch.float32 if config.layer_list else self.torch_dtype
+        self.logits_dtype = torch.bfloat16 if dtype == "f32" else self.torch_dtype
         # torch sees the library's stream as an ExternalStream: tensors handed to the C ABI are allocated
         # on it, so the caching allocator orders their reuse after the kernels that touch them.
         self.torch_stream = torch.cuda.ExternalStream(self.stream_ptr, device=device)
@@ -113,9 +122,9 @@ class Context:
         check(lib().cake_b200_launch_count(self.h, byref(n)))
         return n.value
 
-    def empty(self, *shape) -> torch.Tensor:
+    def empty(self, *shape, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         with torch.cuda.stream(self.torch_stream):
-            return torch.empty(shape, dtype=self.torch_dtype, device=f"cuda:{self.device}")
+            return torch.empty(shape, dtype=dtype or self.torch_dtype, device=f"cuda:{self.device}")
 
     def to_device(self, t: torch.Tensor) -> torch.Tensor:
         """Host tensor (values in D) -> device tensor on the library's stream."""
@@ -249,6 +258,33 @@ class B200Transformer(Forwarder):
             pass
 
 
+class ListedBlock(B200Transformer):
+    """A layer of a layer-list model (``Config.layers``; ``cake_b200_block_load_spec``): same Forwarder surface and the same
+    ``cake_b200_forward_batch`` call as the Llama-family block, with an fp32 activation."""
+
+    @classmethod
+    def load(cls, name: str, ctx: Context) -> "ListedBlock":
+        from .capi import CLayerSpec, CLayerTensors
+        from .loader import LISTED_TENSORS, listed_block_tensors
+        cfg = ctx.config
+        index = [cfg.layer_name(i) for i in range(cfg.num_hidden_layers)].index(name)
+        sp = cfg.layers[index]
+        views = listed_block_tensors(ctx.var_builder, cfg, index)
+        keep = {}
+        for fld, _ in LISTED_TENSORS:
+            t = views[fld]
+            keep[fld] = None if t is None else t.to(ctx.torch_dtype).contiguous()
+        spec = CLayerSpec(sp.heads, sp.kv_heads, sp.head_dim, sp.window, sp.scale, sp.softcap, 1, sp.ff, sp.act, 1)
+        tens = CLayerTensors(*[ptr(keep[fld]) for fld, _ in LISTED_TENSORS])
+        h = c_void_p()
+        check(lib().cake_b200_block_load_spec(ctx.h, index, byref(spec), byref(tens), byref(h)))
+        return cls(name, h, ctx)
+
+
+# Config.block_kind -> the Forwarder that loads and runs its layers
+BLOCK_CLASSES = {"nigenex": ListedBlock}
+
+
 @dataclass
 class Token:
     id: int
@@ -273,20 +309,23 @@ class TextModelBase:
         self._graph_ready = False
 
     @classmethod
-    def load(cls, ctx: Context, block_cls=B200Transformer, make_remote: Optional[Callable] = None, **kw):
+    def load(cls, ctx: Context, block_cls=None, make_remote: Optional[Callable] = None, **kw):
         """text_model.rs:150-264: embed, lm_head (tied -> embed), ln_f, then one block per layer —
-        local ones via Forwarder::load, layers the topology assigns elsewhere via `make_remote`."""
-        cfg, vb, p = ctx.config, ctx.var_builder, ctx.config.model_prefix
+        local ones via Forwarder::load, layers the topology assigns elsewhere via `make_remote`.  The block class follows
+        the config (``BLOCK_CLASSES``) unless one is given."""
+        cfg, vb = ctx.config, ctx.var_builder
+        block_cls = block_cls or BLOCK_CLASSES.get(cfg.block_kind, B200Transformer)
         def get(tname: str, shape):
             t = vb[tname]
             if tuple(t.shape) != tuple(shape):
                 raise ValueError(f"shape mismatch for {tname}, expected: {list(shape)}, got: {list(t.shape)}")
             return t.to(ctx.torch_dtype).contiguous()
 
-        emb = get(f"{p}.embed_tokens.weight", (cfg.vocab_size, cfg.hidden_size))
+        n_emb, n_norm, n_head = cfg.head_tensor_names()
+        emb = get(n_emb, (cfg.vocab_size, cfg.hidden_size))
         from .loader import rms_norm_weight
-        lnf = rms_norm_weight(get(f"{p}.norm.weight", (cfg.hidden_size,)), cfg)   # text_model.rs:186-192
-        head = None if cfg.tie_word_embeddings else get("lm_head.weight", (cfg.vocab_size, cfg.hidden_size))
+        lnf = rms_norm_weight(get(n_norm, () if cfg.layer_list else (cfg.hidden_size,)), cfg)   # text_model.rs:186-192
+        head = None if n_head is None else get(n_head, (cfg.vocab_size, cfg.hidden_size))
         check(lib().cake_b200_head_load(ctx.h, ptr(emb), ptr(lnf), ptr(head)))
         blocks: List[Forwarder] = []
         for i in range(cfg.num_hidden_layers):
@@ -301,12 +340,14 @@ class TextModelBase:
         return cls(ctx, blocks, **kw)
 
     # -- forward (text_model.rs:266-368) ---------------------------------------------------------
-    def forward(self, ids, idx: int) -> torch.Tensor:
-        """ids: (batch, seq) token ids at absolute position idx -> logits (batch, vocab) device tensor in D."""
+    def forward(self, ids, idx: int, want: Optional[Sequence[int]] = None) -> torch.Tensor:
+        """ids: (batch, seq) token ids at absolute position idx -> logits (batch, vocab) device tensor in D.
+        ``want`` (layer-list models): rows b * seq + t whose logits are asked for instead of the last position's ->
+        (len(want), vocab) in fp32; an empty list runs the step for its cache and state only and returns None."""
         ids = np.ascontiguousarray(ids, dtype=np.uint32)
         b, s = ids.shape
         ctx = self.ctx
-        x = ctx.empty(b, s, ctx.config.hidden_size)
+        x = ctx.empty(b, s, ctx.config.hidden_size, dtype=ctx.stream_dtype)
         check(lib().cake_b200_embed(ctx.h, ids.ctypes.data_as(ctypes.POINTER(c_uint32)), b, s, ptr(x)))
         n, i = len(self.blocks), 0
         while i < n:
@@ -321,7 +362,14 @@ class TextModelBase:
             else:
                 x = self.blocks[i].forward_batch(x, group, ctx)
             i = j
-        logits = ctx.empty(b, ctx.config.vocab_size)
+        if want is not None:
+            if not len(want):
+                return None
+            rows = int_array([int(w) for w in want])
+            logits = ctx.empty(len(want), ctx.config.vocab_size, dtype=torch.float32)
+            check(lib().cake_b200_logits_rows(ctx.h, ptr(x), b * s, rows, len(want), ptr(logits)))
+            return logits
+        logits = ctx.empty(b, ctx.config.vocab_size, dtype=ctx.logits_dtype)
         check(lib().cake_b200_logits(ctx.h, ptr(x), b, s, ptr(logits), None))
         return logits
 
@@ -400,6 +448,40 @@ class TextModelBase:
         self.tokens.extend(toks)
         self.generated += n_steps
         return toks
+
+
+class Sessions:
+    """Requests that run one after the other or interleaved over ONE model: every live request id owns a Cache (its K rows
+    and, for layer-list models, its token-shift state); a finished request gives its cache back and the next request reuses
+    it after ``clear()`` (worker.rs:60-75 gives every connection its own cache the same way).  A step feeds the request's
+    next tokens at the position its cache has reached."""
+
+    def __init__(self, model: TextModelBase, max_seq: Optional[int] = None):
+        self.model, self.max_seq = model, max_seq
+        self.live: Dict[str, Cache] = {}
+        self.free: List[Cache] = []
+
+    def cache_of(self, rid: str) -> Cache:
+        c = self.live.get(rid)
+        if c is None:
+            c = self.free.pop() if self.free else Cache(self.model.ctx, 1, self.max_seq)
+            c.clear()
+            self.live[rid] = c
+        return c
+
+    def step(self, rid: str, tokens: Sequence[int], want: Optional[Sequence[int]] = None) -> Optional[torch.Tensor]:
+        cache = self.cache_of(rid)
+        ctx = self.model.ctx
+        prev, ctx.cache = ctx.cache, cache
+        try:
+            return self.model.forward([list(tokens)], cache.len(0), want=want)
+        finally:
+            ctx.cache = prev
+
+    def end(self, rid: str) -> None:
+        c = self.live.pop(rid, None)
+        if c is not None:
+            self.free.append(c)
 
 
 def sampling_from_args(temperature: float, top_k: Optional[int], top_p: Optional[float], seed: int) -> "capi.CSampling":

@@ -52,6 +52,7 @@ extern "C" {
 /* model dtype D (cake/mod.rs:75 --dtype): weights, activations and KV cache are stored in D */
 #define CAKE_B200_BF16 0
 #define CAKE_B200_F16 1
+#define CAKE_B200_F32 2 /* layer-list models only (cake_b200_config.layer_list): weights, activations and cache in true fp32 */
 
 typedef struct cake_b200_ctx cake_b200_ctx;     /* per (process, device): stream, workspaces, graphs, NCCL comm, head weights */
 typedef struct cake_b200_block cake_b200_block; /* immutable weights of one transformer layer */
@@ -75,6 +76,14 @@ typedef struct cake_b200_config {
   float embed_scale;  /* text_model.rs:274-276: x = embedding * scale (0 = none) */
   int pre_reshape_qk_norm; /* config.rs:116, attention.rs:176-192 (OLMo2): QK-norm over the whole q / k projection (weights
                               [n_heads*head_dim] / [n_kv_heads*head_dim]) before the head reshape, instead of per head */
+  /* ---- layer-list models: the checkpoint's config lists its layers one by one, each with its own geometry ----
+   * layer_list = 1: only hidden, n_layers, vocab, max_seq, rms_eps and dtype above are read; every other size comes with
+   * the layer (cake_b200_block_load_spec).  The residual stream of such a model is FP32: x_dev / y_dev of
+   * cake_b200_forward_batch and the output of cake_b200_embed are float, norms and the residual sum are computed in
+   * fp32, and only the operands of the matrix products are in D. */
+  int layer_list;
+  float logit_softcap;   /* logits <- cap * tanh(logits / cap) after the head (0 = none) */
+  int scalar_final_norm; /* the final norm's gain is ONE number (ln_f points to a single element) instead of [hidden] */
 } cake_b200_config;
 
 const char *cake_b200_last_error(void); /* thread-local; valid until the next call on this thread */
@@ -121,6 +130,41 @@ typedef struct cake_b200_block_variant {
 } cake_b200_block_variant;
 int cake_b200_block_set_variant(cake_b200_block *, const cake_b200_block_variant *);
 
+/* ---- layer-list blocks ---------------------------------------------------------------------------
+ * One layer of a model with cake_b200_config.layer_list: a PARALLEL block
+ *     h = norm(x);   x <- x + ( mixer(shift(h)) + ff(h) )
+ * whose mixer is grouped-query attention with the switches below.  Every constant is a parameter so that other
+ * layer lists can combine them differently; a combination that is not built is refused with CAKE_B200_EINVAL.
+ *   norm         RMS norm in fp32, x / sqrt(mean(x^2) + eps) * g, with g one number (scalar_norm) or a [hidden] vector
+ *   token shift  the mixer reads h + (h_prev - h) * shift[hidden] where h_prev is the previous position's h (zeros at
+ *                position 0); the last h of a call is kept per layer in the cache so that a prompt may be cut anywhere
+ *   scores       s = (q . k) * scale;  softcap > 0: s <- softcap * tanh(s / softcap);  distance bias (r1, r2 non-NULL,
+ *                one number per query head): s <- s - r1[h] * ln(1 + r2[h] * (i - j));  window > 0: position i sees
+ *                j with 0 <= i - j < window (0 = every j <= i);  ordinary softmax over the visible keys, all in fp32
+ *   values       values_are_keys: there is no V projection and no V cache; the output is the p-weighted sum of the keys
+ *   head gate    gate non-NULL ([heads, hidden]): head h's output is multiplied by sigmoid(gate_h . shift(h))
+ *   ff           ff > 0: down( act(gate_proj h) * (up h) ), act 0 = silu, 1 = tanh-gelu; ff == 0: no feed-forward
+ * Weights are [out, in] row-major in D (host or device memory), q [heads*head_dim, hidden], k [kv_heads*head_dim, hidden],
+ * o [hidden, heads*head_dim]. */
+typedef struct cake_b200_layer_spec {
+  int heads, kv_heads, head_dim;
+  int window;
+  float scale, softcap;
+  int values_are_keys;
+  int ff, act;
+  int scalar_norm;
+} cake_b200_layer_spec;
+typedef struct cake_b200_layer_tensors {
+  const void *norm;               /* [1] or [hidden] */
+  const void *shift;              /* [hidden] or NULL */
+  const void *q, *k, *v, *o;      /* v must be NULL with values_are_keys */
+  const void *r1, *r2;            /* [heads] or both NULL */
+  const void *gate;               /* [heads, hidden] or NULL */
+  const void *ff_gate, *ff_up, *ff_down; /* [ff, hidden] x2, [hidden, ff]; NULL when ff == 0 */
+} cake_b200_layer_tensors;
+int cake_b200_block_load_spec(cake_b200_ctx *, int layer_idx, const cake_b200_layer_spec *, const cake_b200_layer_tensors *,
+                              cake_b200_block **out);
+
 /* ---- cache ------------------------------------------------------------------------------------ */
 int cake_b200_cache_create(cake_b200_ctx *, int batch, int max_seq, cake_b200_cache **out);
 int cake_b200_cache_clear(cake_b200_cache *);
@@ -152,6 +196,10 @@ int cake_b200_embed(cake_b200_ctx *, const uint32_t *ids_host, int batch, int se
  * logits_dev (nullable); if argmax_host != NULL also computes the greedy token per row
  * (first maximum wins), copies it to argmax_host and synchronises. */
 int cake_b200_logits(cake_b200_ctx *, const void *x_dev, int batch, int seq, void *logits_dev, uint32_t *argmax_host);
+/* The same for ANY rows of x_dev ((n_rows_total, hidden), row = b * seq + t), in FP32: final norm -> lm_head -> logit
+ * soft cap, logits_f32_dev[(i, vocab)] for i < n.  Layer-list models (fp32 residual stream) only.  Asynchronous. */
+int cake_b200_logits_rows(cake_b200_ctx *, const void *x_dev, int n_rows_total, const int *rows_host, int n,
+                          float *logits_f32_dev);
 /* text_model.rs:60-99 repeat penalty on device over logits_dev (vocab) in D, then greedy token. */
 int cake_b200_repeat_penalty_argmax(cake_b200_ctx *, void *logits_dev, float penalty, const uint32_t *ctx_tokens_host,
                                     int n_tokens, uint32_t *argmax_host);
