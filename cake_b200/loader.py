@@ -385,7 +385,7 @@ def save_checkpoint(path: str, cfg: Config, tensors: Dict[str, torch.Tensor], ar
             f.write(blob)
             for n in names:
                 t = tensors[n].detach().cpu().contiguous()
-                f.write(t.view(torch.uint8).numpy().tobytes() if t.numel() else b"")
+                f.write(t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b"")  # reshape: a 0-dim tensor has no byte view
     if files != [SINGLE_NAME]:
         with open(os.path.join(path, INDEX_NAME), "w") as f:
             json.dump({"metadata": {"total_size": sum(t.numel() * t.element_size() for t in tensors.values())},

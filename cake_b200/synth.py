@@ -148,3 +148,30 @@ class LazyCheckpoint(dict):
     def drop_head(self):
         for kk in [kk for kk in self if ".layers." not in kk]:
             del self[kk]
+
+
+def make_listed_checkpoint(cfg: Config, dtype: str = "bf16", seed: int = 1234, device="cpu", std: float = 0.05) -> dict:
+    """Random weights of a layer-list (Nigenex) model under the names its checkpoints use: ``embed``, ``head``,
+    ``final.norm`` (one number) and per layer ``l<i>.norm1`` (one number), ``l<i>.shift`` [width] in (0, 1),
+    ``l<i>.mix.{q,k,o,g}``, ``l<i>.mix.{r1,r2}`` [heads] > 0 and, when the layer has a feed-forward, ``l<i>.mlp.{gate,up,down}``."""
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed * 1000003 + 424243)
+    td, H = TORCH_DTYPES[dtype], cfg.hidden_size
+
+    def rn(*shape, s=std):
+        return (torch.randn(shape, generator=gen, device=device, dtype=torch.float32) * s).to(td)
+
+    def ru(*shape, lo=0.0, hi=1.0):
+        return (torch.rand(shape, generator=gen, device=device, dtype=torch.float32) * (hi - lo) + lo).to(td)
+
+    sd = {"embed": rn(cfg.vocab_size, H, s=1.0), "head": rn(cfg.vocab_size, H, s=4.0 * std), "final.norm": ru(lo=0.8, hi=1.2).reshape(())}
+    for i, sp in enumerate(cfg.layers):
+        p, sq, skv = cfg.layer_name(i), sp.heads * sp.head_dim, sp.kv_heads * sp.head_dim
+        sd[f"{p}.norm1"] = ru(lo=0.8, hi=1.2).reshape(())
+        sd[f"{p}.shift"] = ru(H)
+        sd[f"{p}.mix.q"], sd[f"{p}.mix.k"] = rn(sq, H), rn(skv, H)
+        sd[f"{p}.mix.r1"], sd[f"{p}.mix.r2"] = ru(sp.heads, lo=0.1, hi=1.0), ru(sp.heads, lo=0.05, hi=2.0)
+        sd[f"{p}.mix.g"], sd[f"{p}.mix.o"] = rn(sp.heads, H), rn(H, sq)
+        if sp.ff:
+            sd[f"{p}.mlp.gate"], sd[f"{p}.mlp.up"], sd[f"{p}.mlp.down"] = rn(sp.ff, H), rn(sp.ff, H), rn(H, sp.ff)
+    return sd
