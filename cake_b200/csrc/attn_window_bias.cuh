@@ -13,10 +13,12 @@
 // Kernels:
 //   attn_window_bias_kernel      one warp per (token, head), any head_dim <= 256 and any D (float included): a lane scores
 //                                one key of a 32-key tile, the tile's keys are then accumulated dimension-parallel
-//   attn_window_decode_kernel    one CTA per (batch row, head) for single-token steps: its warps split the window and merge
+//   attn_window_decode_kernel    one CTA per (token, head) for steps of a few tokens: its warps split the window and merge
 //                                their partial softmax states in shared memory
+//   attn_window_mma_kernel       prompt portions on the tensor cores for 16-bit D (below)
 // Nothing here follows a reference file: the reference has none of these modifiers.
 #pragma once
+#include "attn_prefill.cuh"
 #include "common.cuh"
 #include "f32_stream.cuh"
 
@@ -69,6 +71,38 @@ __device__ __forceinline__ float wa_score(float dot, const WinAttn &p, float r1,
   return s;
 }
 
+// One warp's scan over the key tiles lo + 32 * (first + k * step), k = 0, 1, ...: running max m, sum l and the weighted sum
+// of values acc[i] for dimension lane + 32 i.  q sits in shared memory as fp32.
+template <typename T>
+__device__ __forceinline__ void wa_scan(const WinAttn &p, const float *q, const T *kc, const T *vc, int lo, int pi, int first, int step,
+                                        float r1, float r2, bool biased, int lane, float &m, float &l, float (&acc)[WA_MAX_HD / 32]) {
+  constexpr int MAXD = WA_MAX_HD / 32;
+  const int hd = p.hd;
+  for (int j0 = lo + 32 * first; j0 <= pi; j0 += 32 * step) {
+    const int j = j0 + lane;
+    const bool vis = j <= pi;
+    float s = -INFINITY;
+    if (vis) s = wa_score(wa_dot<T>(q, kc + (size_t)j * hd, hd), p, r1, r2, biased, pi, j);
+    const float mn = fmaxf(m, warp_max(s));
+    const float f = (m == -INFINITY) ? 0.f : expf(m - mn);
+    const float e = vis ? expf(s - mn) : 0.f;
+    l = l * f + warp_sum(e);
+    m = mn;
+#pragma unroll
+    for (int i = 0; i < MAXD; i++) acc[i] *= f;
+    const int cnt = min(32, pi - j0 + 1);
+    for (int jj = 0; jj < cnt; jj++) {
+      const float pj = __shfl_sync(0xffffffffu, e, jj);
+      const T *vr = vc + (size_t)(j0 + jj) * hd;
+#pragma unroll
+      for (int i = 0; i < MAXD; i++) {
+        const int d = lane + 32 * i;
+        if (d < hd) acc[i] = fmaf(pj, DT<T>::to_f(vr[d]), acc[i]);
+      }
+    }
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(128) attn_window_bias_kernel(const WinAttn p) {
   pdl_launch_dependents();
@@ -96,29 +130,7 @@ __global__ void __launch_bounds__(128) attn_window_bias_kernel(const WinAttn p) 
 #pragma unroll
   for (int i = 0; i < MAXD; i++) acc[i] = 0.f;
   float m = -INFINITY, l = 0.f;
-  for (int j0 = lo; j0 <= pi; j0 += 32) {
-    const int j = j0 + lane;
-    const bool vis = j <= pi;
-    float s = -INFINITY;
-    if (vis) s = wa_score(wa_dot<T>(qs[warp], kc + (size_t)j * hd, hd), p, r1, r2, biased, pi, j);
-    const float mn = fmaxf(m, warp_max(s));
-    const float f = (m == -INFINITY) ? 0.f : expf(m - mn);
-    const float e = vis ? expf(s - mn) : 0.f;
-    l = l * f + warp_sum(e);
-    m = mn;
-#pragma unroll
-    for (int i = 0; i < MAXD; i++) acc[i] *= f;
-    const int cnt = min(32, pi - j0 + 1);
-    for (int jj = 0; jj < cnt; jj++) {
-      const float pj = __shfl_sync(0xffffffffu, e, jj);
-      const T *vr = vc + (size_t)(j0 + jj) * hd;
-#pragma unroll
-      for (int i = 0; i < MAXD; i++) {
-        const int d = lane + 32 * i;
-        if (d < hd) acc[i] = fmaf(pj, DT<T>::to_f(vr[d]), acc[i]);
-      }
-    }
-  }
+  wa_scan<T>(p, qs[warp], kc, vc, lo, pi, 0, 1, r1, r2, biased, lane, m, l, acc);
   float gate = 1.0f;
   if (p.gate_col >= 0) gate = 1.0f / (1.0f + expf(-DT<T>::to_f(qrow[p.gate_col + h])));
   const float inv = gate / l;
@@ -127,6 +139,225 @@ __global__ void __launch_bounds__(128) attn_window_bias_kernel(const WinAttn p) 
   for (int i = 0; i < MAXD; i++) {
     const int d = lane + 32 * i;
     if (d < hd) yo[d] = DT<T>::from_f(acc[i] * inv);
+  }
+}
+
+// Single-token steps: one CTA per (token, head); its 8 warps take the window's 32-key tiles in turn and merge their
+// (m, l, acc) states in shared memory in warp order, so the result does not depend on timing.
+constexpr int WA_DEC_WARPS = 8;
+template <typename T>
+__global__ void __launch_bounds__(WA_DEC_WARPS * 32) attn_window_decode_kernel(const WinAttn p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float qs[WA_MAX_HD];
+  __shared__ float sm_m[WA_DEC_WARPS], sm_l[WA_DEC_WARPS];
+  __shared__ float sm_acc[WA_DEC_WARPS][WA_MAX_HD];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int item = blockIdx.x;
+  const int h = item % p.heads, t = (item / p.heads) % p.S, b = item / (p.heads * p.S);
+  const int hd = p.hd, G = p.heads / p.n_kv;
+  const T *qrow = reinterpret_cast<const T *>(p.qkg) + (size_t)(b * p.S + t) * p.ld;
+  const T *kc = reinterpret_cast<const T *>(p.kc) + ((size_t)b * p.n_kv + h / G) * p.cap * hd;
+  const T *vc = reinterpret_cast<const T *>(p.vc) + ((size_t)b * p.n_kv + h / G) * p.cap * hd;
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) qs[d] = DT<T>::to_f(qrow[h * hd + d]);
+  __syncthreads();
+  const bool biased = p.r1 != nullptr;
+  const float r1 = biased ? DT<T>::to_f(reinterpret_cast<const T *>(p.r1)[h]) : 0.f;
+  const float r2 = biased ? DT<T>::to_f(reinterpret_cast<const T *>(p.r2)[h]) : 0.f;
+  const int pi = p.pos0 + t;
+  const int lo = p.window > 0 ? max(0, pi - p.window + 1) : 0;
+  constexpr int MAXD = WA_MAX_HD / 32;
+  float acc[MAXD];
+#pragma unroll
+  for (int i = 0; i < MAXD; i++) acc[i] = 0.f;
+  float m = -INFINITY, l = 0.f;
+  wa_scan<T>(p, qs, kc, vc, lo, pi, warp, WA_DEC_WARPS, r1, r2, biased, lane, m, l, acc);
+  if (lane == 0) { sm_m[warp] = m; sm_l[warp] = l; }
+#pragma unroll
+  for (int i = 0; i < MAXD; i++) {
+    const int d = lane + 32 * i;
+    if (d < hd) sm_acc[warp][d] = acc[i];
+  }
+  __syncthreads();
+  float mx = -INFINITY;
+  for (int w = 0; w < WA_DEC_WARPS; w++) mx = fmaxf(mx, sm_m[w]);
+  float lt = 0.f;
+  for (int w = 0; w < WA_DEC_WARPS; w++) lt += sm_m[w] == -INFINITY ? 0.f : sm_l[w] * expf(sm_m[w] - mx);
+  float gate = 1.0f;
+  if (p.gate_col >= 0) gate = 1.0f / (1.0f + expf(-DT<T>::to_f(qrow[p.gate_col + h])));
+  const float inv = gate / lt;
+  T *yo = reinterpret_cast<T *>(p.y) + (size_t)(b * p.S + t) * p.ldy + h * hd;
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    float a = 0.f;
+    for (int w = 0; w < WA_DEC_WARPS; w++)
+      if (sm_m[w] != -INFINITY) a = fmaf(sm_acc[w][d], expf(sm_m[w] - mx), a);
+    yo[d] = DT<T>::from_f(a * inv);
+  }
+}
+
+// ---- prompt portions on the tensor cores (16-bit D, head_dim a multiple of 16) -----------------------------------------------
+// Flash-style like attn_prefill_mma_kernel (attn_prefill.cuh): a CTA = 64 query rows of one head (4 warps x 16 rows), key
+// tiles of 64 positions through a 2-stage cp.async pipeline, mma.sync m16n8k16 with fp32 accumulation, P = P_hi + P_lo in D.
+// Differences: the tile loop starts at the first tile the window reaches; the score gets its soft cap and distance bias
+// before the mask; ONE shared-memory tile is both the K operand of Q K^T and — read with ldmatrix.trans — the V operand of
+// P V, since the values are the keys; the head gate scales the result.  Rows are padded by 16 bytes (an odd number of
+// 16-byte chunks per row keeps ldmatrix conflict-free for every head_dim, also those that are not a power of two).
+// tanh and ln use the MUFU-based __expf / __logf: |error| ~1e-6 of the score, two orders below the rounding of q and k to D.
+constexpr int WM_BM = 64, WM_BN = 64, WM_THREADS = 128;
+template <int HD> __device__ __forceinline__ uint32_t wm_off(int r, int c) { return (uint32_t)(r * (HD * 2 + 16) + (c << 4)); }
+template <int HD> constexpr int wm_smem_bytes() { return 3 * WM_BN * (HD * 2 + 16); }
+
+template <typename T, int HD>
+__global__ void __launch_bounds__(WM_THREADS, 2) attn_window_mma_kernel(const WinAttn p) {
+  constexpr int CH = HD / 8, KS = HD / 16, NT = WM_BN / 8, DTN = HD / 8;
+  constexpr int TILE_B = WM_BN * (HD * 2 + 16);
+  extern __shared__ __align__(128) unsigned char wm_smem[];
+  unsigned char *k_s = wm_smem;               // [2][64][HD + 8]
+  unsigned char *q_s = wm_smem + 2 * TILE_B;  // [64][HD + 8]
+  pdl_launch_dependents();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int mt = gridDim.x - 1 - blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z, G = p.heads / p.n_kv;
+  const int m0 = mt * WM_BM;
+  const T *qkg = reinterpret_cast<const T *>(p.qkg);
+  const T *kc = reinterpret_cast<const T *>(p.kc) + ((size_t)b * p.n_kv + h / G) * p.cap * HD;
+  const int kv_end = p.pos0 + min(p.S, m0 + WM_BM);                                    // one past the last key this tile's rows see
+  const int k_first = p.window > 0 ? max(0, p.pos0 + m0 - p.window + 1) : 0;          // first key its first row sees
+  const int j_lo = k_first / WM_BN, n_tiles = (kv_end + WM_BN - 1) / WM_BN;
+
+  auto load_k = [&](int j, int buf) {
+    for (int i = threadIdx.x; i < WM_BN * CH; i += WM_THREADS) {
+      const int r = i / CH, c = i % CH, key = j * WM_BN + r;
+      const bool ok = key < kv_end;
+      cp_async16(smem_u32(k_s + buf * TILE_B) + wm_off<HD>(r, c), kc + (size_t)(ok ? key : 0) * HD + c * 8, ok ? 16 : 0);
+    }
+  };
+  for (int i = threadIdx.x; i < WM_BM * CH; i += WM_THREADS) {
+    const int r = i / CH, c = i % CH, t = m0 + r;
+    const bool ok = t < p.S;
+    cp_async16(smem_u32(q_s) + wm_off<HD>(r, c), qkg + (size_t)(b * p.S + (ok ? t : 0)) * p.ld + h * HD + c * 8, ok ? 16 : 0);
+  }
+  load_k(j_lo, 0);
+  cp_async_commit();
+
+  float o[DTN][4];
+#pragma unroll
+  for (int i = 0; i < DTN; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  uint32_t qf[KS][4];
+  const int g = lane >> 2, c2 = (lane & 3) * 2;
+  const int qpos0 = p.pos0 + m0 + warp * 16 + g;
+  const int mi = lane >> 3, lr = lane & 7;
+  const bool biased = p.r1 != nullptr;
+  const float r1 = biased ? DT<T>::to_f(reinterpret_cast<const T *>(p.r1)[h]) : 0.f;
+  const float r2 = biased ? DT<T>::to_f(reinterpret_cast<const T *>(p.r2)[h]) : 0.f;
+  const float inv_cap2 = p.softcap > 0.f ? 2.0f / p.softcap : 0.f;
+
+  cp_async_wait<0>();
+  __syncthreads();
+#pragma unroll
+  for (int ks = 0; ks < KS; ks++) ldsm_x4(qf[ks], smem_u32(q_s) + wm_off<HD>(warp * 16 + (mi & 1) * 8 + lr, ks * 2 + (mi >> 1)));
+  for (int j = j_lo; j < n_tiles; j++) {
+    const int buf = (j - j_lo) & 1;
+    if (j + 1 < n_tiles) load_k(j + 1, buf ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    float s[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+    const uint32_t kb_addr = smem_u32(k_s + buf * TILE_B);
+#pragma unroll
+    for (int ks = 0; ks < KS; ks++) {
+#pragma unroll
+      for (int np = 0; np < NT / 2; np++) {
+        uint32_t kf[4];
+        ldsm_x4(kf, kb_addr + wm_off<HD>(np * 16 + (mi >> 1) * 8 + lr, ks * 2 + (mi & 1)));
+        FaMma<T>::mma(s[2 * np], qf[ks], kf[0], kf[1]);
+        FaMma<T>::mma(s[2 * np + 1], qf[ks], kf[2], kf[3]);
+      }
+    }
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        const int key = j * WM_BN + nt * 8 + c2 + (e & 1);
+        const int d = qpos0 + (e >> 1) * 8 - key;
+        float v = -INFINITY;
+        if (d >= 0 && (p.window == 0 || d < p.window)) {
+          v = s[nt][e] * p.scale;
+          if (p.softcap > 0.f) v = p.softcap * (1.0f - __fdividef(2.0f, __expf(v * inv_cap2) + 1.0f));
+          if (biased) v -= r1 * __logf(1.0f + r2 * (float)d);
+        }
+        s[nt][e] = v;
+        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+      }
+    float fac[2], rs[2] = {0.f, 0.f};
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+      const float mn = fmaxf(m_run[r], mx[r]);
+      fac[r] = (m_run[r] == -INFINITY) ? 0.f : __expf(m_run[r] - mn);
+      m_run[r] = mn;
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        const float mn = m_run[e >> 1];
+        const float pv = (mn == -INFINITY) ? 0.f : __expf(s[nt][e] - mn);
+        s[nt][e] = pv;
+        rs[e >> 1] += pv;
+      }
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+      rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 1);
+      rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 2);
+      l_run[r] = l_run[r] * fac[r] + rs[r];
+    }
+#pragma unroll
+    for (int dt = 0; dt < DTN; dt++) {
+      o[dt][0] *= fac[0]; o[dt][1] *= fac[0]; o[dt][2] *= fac[1]; o[dt][3] *= fac[1];
+    }
+#pragma unroll
+    for (int kb = 0; kb < WM_BN / 16; kb++) {
+      uint32_t ph[4], pl[4];
+#pragma unroll
+      for (int q = 0; q < 4; q++) {
+        const float p0 = s[2 * kb + (q >> 1)][(q & 1) * 2], p1 = s[2 * kb + (q >> 1)][(q & 1) * 2 + 1];
+        const float h0 = rnd<T>(p0), h1 = rnd<T>(p1);
+        ph[q] = pack2<T>(h0, h1);
+        pl[q] = pack2<T>(p0 - h0, p1 - h1);
+      }
+#pragma unroll
+      for (int dp = 0; dp < DTN / 2; dp++) {
+        uint32_t vf[4];
+        ldsm_x4_trans(vf, kb_addr + wm_off<HD>(kb * 16 + (mi & 1) * 8 + lr, dp * 2 + (mi >> 1)));
+        FaMma<T>::mma(o[2 * dp], ph, vf[0], vf[1]);
+        FaMma<T>::mma(o[2 * dp], pl, vf[0], vf[1]);
+        FaMma<T>::mma(o[2 * dp + 1], ph, vf[2], vf[3]);
+        FaMma<T>::mma(o[2 * dp + 1], pl, vf[2], vf[3]);
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int r = 0; r < 2; r++) {
+    const int t = m0 + warp * 16 + g + r * 8;
+    if (t < p.S) {
+      const T *qrow = qkg + (size_t)(b * p.S + t) * p.ld;
+      float gate = 1.0f;
+      if (p.gate_col >= 0) gate = 1.0f / (1.0f + expf(-DT<T>::to_f(qrow[p.gate_col + h])));
+      const float inv = gate / l_run[r];
+      T *dst = reinterpret_cast<T *>(p.y) + (size_t)(b * p.S + t) * p.ldy + h * HD;
+#pragma unroll
+      for (int dt = 0; dt < DTN; dt++)
+        *reinterpret_cast<uint32_t *>(dst + dt * 8 + c2) = pack2<T>(o[dt][2 * r] * inv, o[dt][2 * r + 1] * inv);
+    }
   }
 }
 

@@ -352,7 +352,10 @@ template <typename T> static int set_smem_attrs_T() {
   CU(cudaFuncSetAttribute(gemm_tc_kernel<T, EPI, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<128>::SMEM_BYTES));      \
   CU(cudaFuncSetAttribute(gemm_tc_kernel<T, EPI, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<256>::SMEM_BYTES));      \
   CU(cudaFuncSetAttribute(gemm_tc_kernel<T, EPI, 256, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<256>::SMEM_BYTES));
-  SETT(TCE_PLAIN) SETT(TCE_RESIDUAL) SETT(TCE_SWIGLU)
+  SETT(TCE_PLAIN) SETT(TCE_RESIDUAL) SETT(TCE_SWIGLU) SETT(TCE_RESIDUAL_F32)
+#define SETW(HD) CU(cudaFuncSetAttribute(attn_window_mma_kernel<T, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, wm_smem_bytes<HD>()));
+  SETW(32) SETW(64) SETW(96) SETW(128)
+#undef SETW
 #undef SETT
   return CAKE_B200_OK;
 }
@@ -1124,7 +1127,8 @@ static bool tc_gemm_ok(int M, int N, int K) { return M >= 1 && N % TC_BN == 0 &&
 
 // C = epi(A[M,K] W[N,K]^T) on the tensor cores (gemm_tc.cuh)
 template <typename T, int EPI>
-static int gemm_tc_T(cake_b200_ctx *c, const void *A, const void *W, const void *bias, const void *res, void *C, int M, int N, int K) {
+static int gemm_tc_T(cake_b200_ctx *c, const void *A, const void *W, const void *bias, const void *res, void *C, int M, int N, int K,
+                     int act = -1, int ldc = 0) {
   // 128 x 256 tiles when N allows and there are enough tiles to fill the chip; CAKE_B200_TC_BN=128 forces the small tile (A/B aid)
   static const int force_bn = []() { const char *e = getenv("CAKE_B200_TC_BN"); return e ? atoi(e) : 0; }();
   const int tiles_m = (M + TC_BM - 1) / TC_BM;
@@ -1136,7 +1140,7 @@ static int gemm_tc_T(cake_b200_ctx *c, const void *A, const void *W, const void 
   CUtensorMap ma, mb;
   RC(make_tmap(&ma, A, (uint64_t)M, (uint64_t)K, c->cfg.dtype, TC_BM));
   RC(make_tmap(&mb, W, (uint64_t)N, (uint64_t)K, c->cfg.dtype, mc ? 128u : (uint32_t)bn));
-  TcParams p{bias, res, C, M, N, K, c->cfg.use_gelu_mlp ? 1 : 0};
+  TcParams p{bias, res, C, M, N, K, act >= 0 ? act : (c->cfg.use_gelu_mlp ? 1 : 0), ldc};
   const int tiles = tiles_m * (N / bn);
   dim3 grid(tiles < c->sm_count ? tiles : c->sm_count), block(TC_THREADS);
   if (mc) {
@@ -1389,6 +1393,48 @@ static int sp_reserve(cake_b200_ctx *c, size_t rows, size_t in_cols, size_t out_
   return CAKE_B200_OK;
 }
 
+// the tcgen05 GEMM takes a product of a layer-list block when D is 16-bit and its tiles cover the shape (N % 128, K % 64);
+// CAKE_B200_NO_TC=1 keeps the CUDA-core kernel (A/B aid).  D = float always runs true fp32 on the CUDA cores.
+template <typename T> static bool listed_tc(cake_b200_ctx *, int M, int N, int K) {
+  static const bool no_tc = []() { const char *e = getenv("CAKE_B200_NO_TC"); return e && e[0] == '1'; }();
+  return !no_tc && tc_gemm_ok(M, N, K);
+}
+template <> bool listed_tc<float>(cake_b200_ctx *, int, int, int) { return false; }
+template <typename T, int EPI>
+static int listed_gemm_tc(cake_b200_ctx *c, const void *A, const void *W, const void *res, void *C, int M, int N, int K, int act, int ldc) {
+  return gemm_tc_T<T, EPI>(c, A, W, nullptr, res, C, M, N, K, act, ldc);
+}
+template <> int listed_gemm_tc<float, TCE_PLAIN>(cake_b200_ctx *, const void *, const void *, const void *, void *, int, int, int, int, int) { return CAKE_B200_EINVAL; }
+template <> int listed_gemm_tc<float, TCE_SWIGLU>(cake_b200_ctx *, const void *, const void *, const void *, void *, int, int, int, int, int) { return CAKE_B200_EINVAL; }
+template <> int listed_gemm_tc<float, TCE_RESIDUAL_F32>(cake_b200_ctx *, const void *, const void *, const void *, void *, int, int, int, int, int) { return CAKE_B200_EINVAL; }
+
+// attention of a layer-list block: tensor cores for prompt portions in 16-bit D, the warp-split kernel for steps of a few
+// tokens, the warp-per-row kernel for everything else (any head_dim, D = float)
+template <typename T> static int listed_attention_mma(cake_b200_ctx *c, const WinAttn &wa, bool *done) {
+  *done = true;
+  dim3 grid((wa.S + WM_BM - 1) / WM_BM, wa.heads, wa.B), block(WM_THREADS);
+  switch (wa.hd) {
+    case 32: return launch_pdl(c, attn_window_mma_kernel<T, 32>, grid, block, (size_t)wm_smem_bytes<32>(), wa);
+    case 64: return launch_pdl(c, attn_window_mma_kernel<T, 64>, grid, block, (size_t)wm_smem_bytes<64>(), wa);
+    case 96: return launch_pdl(c, attn_window_mma_kernel<T, 96>, grid, block, (size_t)wm_smem_bytes<96>(), wa);
+    case 128: return launch_pdl(c, attn_window_mma_kernel<T, 128>, grid, block, (size_t)wm_smem_bytes<128>(), wa);
+  }
+  *done = false;
+  return CAKE_B200_OK;
+}
+template <> int listed_attention_mma<float>(cake_b200_ctx *, const WinAttn &, bool *done) { *done = false; return CAKE_B200_OK; }
+template <typename T> static int listed_attention(cake_b200_ctx *c, const WinAttn &wa) {
+  static const bool no_mma = []() { const char *e = getenv("CAKE_B200_NO_TC"); return e && e[0] == '1'; }();
+  const long items = (long)wa.B * wa.S * wa.heads;
+  if (wa.S >= 16 && !no_mma && wa.ld % 8 == 0 && wa.ldy % 2 == 0) {
+    bool done = false;
+    RC(listed_attention_mma<T>(c, wa, &done));
+    if (done) return CAKE_B200_OK;
+  }
+  if (wa.S <= 8) return launch_pdl(c, attn_window_decode_kernel<T>, dim3((unsigned)items), dim3(WA_DEC_WARPS * 32), 0, wa);
+  return launch_pdl(c, attn_window_bias_kernel<T>, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, wa);
+}
+
 template <typename T, int EPI> static int gemm_rows_T(cake_b200_ctx *c, const RowsGemm &g) {
   dim3 grid((g.N + RG_BN - 1) / RG_BN, (g.M + RG_BM - 1) / RG_BM), block(256);
   return launch_pdl(c, gemm_rows_kernel<T, EPI>, grid, block, 0, g);
@@ -1420,22 +1466,26 @@ static int enqueue_listed_layers(cake_b200_ctx *c, cake_b200_block *const *block
                     c->cfg.rms_eps, pos0));
       // 2. q | k | gate logits in one product
       RowsGemm gi{mix_in, b->w_in, nullptr, c->sp_in, M, b->n_in, H, H, b->n_in_pad, 0, 0.f};
-      RC((gemm_rows_T<T, RE_STORE>(c, gi)));
+      if (listed_tc<T>(c, M, b->n_in_pad, H)) RC((listed_gemm_tc<T, TCE_PLAIN>(c, mix_in, b->w_in, nullptr, c->sp_in, M, b->n_in_pad, H, 0, 0)));
+      else RC((gemm_rows_T<T, RE_STORE>(c, gi)));
       // 3. the step's keys join the cache, then attention reads keys (= values) only from there
       RC(launch_pdl(c, rows_to_cache_kernel<T>, dim3(M), dim3(128), 0, (const T *)c->sp_in, (T *)kc->k[l], S, b->n_in_pad, sq, sp.kv_heads, hd,
                     kc->cap, pos0));
       WinAttn wa{c->sp_in, kc->k[l], kc->k[l], b->r1, b->r2, c->sp_a, B, S, sp.heads, sp.kv_heads, hd, kc->cap, pos0, b->n_in_pad, b->k_out,
                  b->gate_col, sp.window, sp.scale, sp.softcap};
-      const long items = (long)M * sp.heads;
-      RC(launch_pdl(c, attn_window_bias_kernel<T>, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, wa));
+      RC(listed_attention<T>(c, wa));
       // 4. feed-forward input half: act(gate h) * (up h), written next to the attention output
       if (sp.ff > 0) {
         RowsGemm gu{c->sp_h, b->wgu, nullptr, (T *)c->sp_a + sq, M, 2 * sp.ff, H, H, b->k_out, sp.act, 0.f};
-        RC((gemm_rows_T<T, RE_GATE_UP>(c, gu)));
+        if (listed_tc<T>(c, M, 2 * sp.ff, H) && sq % 8 == 0 && b->k_out % 8 == 0)
+          RC((listed_gemm_tc<T, TCE_SWIGLU>(c, c->sp_h, b->wgu, nullptr, (T *)c->sp_a + sq, M, 2 * sp.ff, H, sp.act, b->k_out)));
+        else RC((gemm_rows_T<T, RE_GATE_UP>(c, gu)));
       }
       // 5. x <- x + [attention | ff] . [o | down]^T
       RowsGemm go{c->sp_a, b->w_out, cur, x_out, M, H, b->k_out, b->k_out, H, 0, 0.f};
-      RC((gemm_rows_T<T, RE_RESIDUAL_F32>(c, go)));
+      if (listed_tc<T>(c, M, H, b->k_out) && (((uintptr_t)cur | (uintptr_t)x_out) & 15) == 0)
+        RC((listed_gemm_tc<T, TCE_RESIDUAL_F32>(c, c->sp_a, b->w_out, cur, x_out, M, H, b->k_out, 0, 0)));
+      else RC((gemm_rows_T<T, RE_RESIDUAL_F32>(c, go)));
       cur = x_out;
     }
     return CAKE_B200_OK;
