@@ -7,6 +7,7 @@ Llama-3-8B bf16, bs=1, 2k context, layers sharded over N GPUs of one box (N=1 ->
     torchrun --nproc-per-node N bench.py --gpus N ...             # N > 1, one rank per GPU
     python bench.py --model 70b [--gpus N]                        # BASELINE configs[3] as the main line
     python bench.py --workload prefill                            # BASELINE configs[4] as the main line
+    python bench.py --workload nigenex [--sizes 2k,4k,4k-hd64]    # the Nigenex design beside the closest existing block
 
 A "step" is one decoded token: one pass of the hot path (embed -> blocks -> ln_f/lm_head/argmax) at batch 1.
 tok/s follows the reference's definition (master.rs:131-166): prefill excluded.  Prints ONE JSON line (rank 0).
@@ -891,12 +892,139 @@ def prefill_leg(env: Env, reps: int = 3, batch: int = 32, seq: int = 4096) -> di
     return res
 
 
+
+# ------------------------------------------------------------------------------------------------
+NIGENEX_SIZES = {  # layer sizes of real models, 4 layers each (random weights): width, heads, kv_heads, head_dim, ff, window
+    "2k": dict(width=2048, heads=16, kv_heads=4, head_dim=128, ff=8192, window=1024),
+    "4k": dict(width=4096, heads=32, kv_heads=8, head_dim=128, ff=14336, window=1024),
+    "4k-hd64": dict(width=4096, heads=64, kv_heads=8, head_dim=64, ff=14336, window=1024),
+}
+
+
+def nigenex_leg(env: Env, sizes=("2k", "4k", "4k-hd64"), n_layers: int = 4, batch: int = 4, seq: int = 4096, ctx_len: int = 2048,
+                steps: int = 32, reps: int = 3) -> dict:
+    """`--workload nigenex`: the Nigenex design (layer-list blocks, fp32 residual stream) beside the framework's closest
+    existing model at equal layer sizes — the Gemma3-style block (per-layer sliding window without RoPE, tanh-gelu MLP,
+    stepped through the same batched path) — both through TextModelBase / forward_batch:
+      prefill   one step of batch x seq tokens from an empty cache through all layers + the head on the last positions
+      decode    bs=1: a ctx_len-token prompt, then `steps` single-token steps (embed -> layers -> head), timed as a whole
+    Device time by CUDA events on the library's stream.  L2: the step's activations (prefill) / the layers' weights (decode)
+    exceed the 126 MB L2 at every size."""
+    import torch
+    from cake_b200.capi import check, lib, ptr
+    from cake_b200.config import Config, LayerSpec
+    from cake_b200.model import Cache, Context, TextModelBase
+    from cake_b200.synth import make_checkpoint, make_listed_checkpoint
+    pk = peaks()
+    out = {}
+    launches = 0
+    for name in sizes:
+        z = NIGENEX_SIZES[name]
+        W, nh, nkv, hd, ff, win = z["width"], z["heads"], z["kv_heads"], z["head_dim"], z["ff"], z["window"]
+        vocab = 32768
+        row = {"size": z}
+        for arch in ("nigenex", "closest"):
+            if arch == "nigenex":
+                spec = LayerSpec(heads=nh, kv_heads=nkv, head_dim=hd, window=win, scale=hd ** -0.5, softcap=30.0, ff=ff)
+                cfg = Config(hidden_size=W, intermediate_size=ff, vocab_size=vocab, num_hidden_layers=n_layers, num_attention_heads=nh,
+                             num_key_value_heads=nkv, head_dim=hd, max_seq_len=seq, block_kind="nigenex", layers=[spec] * n_layers,
+                             logit_softcap=30.0, model_prefix="")
+                sd = make_listed_checkpoint(cfg, "bf16", seed=5, device=env.dev, std=0.02)
+                n_in = (nh + nkv) * hd + nh
+                flop_lin = 2.0 * W * (n_in + 2 * ff + nh * hd + ff)
+                wbytes = 2.0 * W * (n_in + 3 * ff + nh * hd)
+                att_keys = lambda S: sum(min(i + 1, win) for i in range(S))
+            else:
+                cfg = Config(hidden_size=W, intermediate_size=ff, vocab_size=vocab, num_hidden_layers=n_layers, num_attention_heads=nh,
+                             num_key_value_heads=nkv, head_dim=hd, max_seq_len=seq, block_kind="gemma3", sliding_window=win,
+                             global_layers=[False] * n_layers, use_qk_norm=True, use_gelu_mlp=True, tie_word_embeddings=True)
+                sd = make_checkpoint(cfg, "bf16", seed=5, device=env.dev, std=0.02)
+                flop_lin = 2.0 * W * ((nh + 2 * nkv) * hd + 2 * ff + nh * hd + ff)
+                wbytes = 2.0 * W * ((nh + 2 * nkv) * hd + 3 * ff + nh * hd)
+                att_keys = lambda S: S * (S + 1) // 2   # the first call on an empty cache attends over everything it stores (cache.rs:173-205)
+            ctx = Context(cfg, sd, "bf16", device=env.local, max_seq=seq)
+            model = TextModelBase.load(ctx)
+            del sd
+            torch.cuda.empty_cache()
+            blks = model.blocks
+            bl = [(b.layer_name(), 0, i) for i, b in enumerate(blks)]
+            # ---- prefill
+            ctx.cache = Cache(ctx, batch, seq)
+            with torch.cuda.stream(ctx.torch_stream):
+                g = torch.Generator(device=env.dev).manual_seed(11)
+                x = (torch.randn(batch, seq, W, generator=g, device=env.dev) * 0.5).to(ctx.stream_dtype)
+                logits = torch.empty(batch, vocab, dtype=ctx.logits_dtype, device=env.dev)
+            times = []
+            for r in range(reps + 1):
+                ctx.cache.clear()
+                ctx.sync()
+                l0 = ctx.launch_count()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(ctx.torch_stream)
+                y = blks[0].forward_batch(x, bl, ctx, blocks=blks)
+                check(lib().cake_b200_logits(ctx.h, ptr(y), batch, seq, ptr(logits), None))
+                e1.record(ctx.torch_stream)
+                ctx.sync()
+                if r > 0:
+                    times.append(e0.elapsed_time(e1))
+                    launches += ctx.launch_count() - l0
+            ms = statistics.median(times)
+            M = batch * seq
+            flops = n_layers * (flop_lin * M + 4.0 * nh * hd * batch * att_keys(seq)) + 2.0 * batch * vocab * W
+            pre = {"tok_s": M / (ms / 1e3), "ms": ms, "tflops": flops / (ms * 1e-3) / 1e12,
+                   "frac_of_tensor_peak": flops / (ms * 1e-3) / 1e12 / pk["tc"], "finite": bool(torch.isfinite(logits.float()).all())}
+            del x, y
+            # ---- decode
+            ctx.cache = Cache(ctx, 1, seq)
+            ids = torch.randint(0, vocab, (ctx_len + steps + 3,), generator=torch.Generator().manual_seed(3)).tolist()
+            model.forward([ids[:ctx_len]], 0)
+            pos = ctx_len
+            for _ in range(3):
+                model.forward([[ids[pos]]], pos)
+                pos += 1
+            ctx.sync()
+            l0 = ctx.launch_count()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(ctx.torch_stream)
+            for _ in range(steps):
+                lg = model.forward([[ids[pos]]], pos)
+                pos += 1
+            e1.record(ctx.torch_stream)
+            ctx.sync()
+            launches += ctx.launch_count() - l0
+            dms = e0.elapsed_time(e1) / steps
+            dbytes = n_layers * (wbytes + 2.0 * nkv * hd * min(win, ctx_len) * (1 if arch == "nigenex" else 2)) + 2.0 * vocab * W
+            dec = {"tok_s": 1e3 / dms, "ms_per_token": dms, "gb_s": dbytes / (dms * 1e-3) / 1e9, "frac_of_hbm_peak": dbytes / (dms * 1e-3) / 1e9 / pk["hbm"],
+                   "finite": bool(torch.isfinite(lg.float()).all())}
+            row[arch] = {"prefill": pre, "decode": dec}
+            ctx.close()
+            del model, blks, ctx
+            torch.cuda.empty_cache()
+        row["prefill_ratio"] = row["nigenex"]["prefill"]["tok_s"] / row["closest"]["prefill"]["tok_s"]
+        row["decode_ratio"] = row["nigenex"]["decode"]["tok_s"] / row["closest"]["decode"]["tok_s"]
+        out[name] = row
+    head = out[sizes[-1] if "4k" not in out else "4k"]
+    return {"metric": "nigenex prefill tok/s (4 layers of Llama-3-8B size, bf16, bs=4 x 4096)", "value": head["nigenex"]["prefill"]["tok_s"],
+            "unit": "tok/s", "ms_per_step": head["nigenex"]["prefill"]["ms"], "steps": reps, "warmup": 1, "gpu_launches": int(launches),
+            "config": {"workload": f"Nigenex vs the Gemma3-style windowed block at equal sizes, {n_layers} layers, bf16, prefill bs={batch} x {seq}, "
+                                   f"decode bs=1 at {ctx_len} context x {steps} steps", "l2": "prefill activations / decode weights exceed L2"},
+            "peaks": {"tensor_tflops": pk["tc"], "hbm_gbs": pk["hbm"], "source": pk["src"]}, "sizes": out}
+
 # ------------------------------------------------------------------------------------------------
 def run_cuda(args):
     env = Env(args)
     K, W = args.steps, max(args.warmup, 3)
     world, rank = env.world, env.rank
     extras = args.extras
+    if args.workload == "nigenex":
+        if rank == 0:
+            if env.sampler:
+                env.sampler.start()
+            line = nigenex_leg(env, sizes=tuple(args.sizes.split(",")), steps=max(4, min(args.steps, 64)))
+            line["clocks"] = env.sampler.stop() if env.sampler else None
+            line.update({"n_gpus": 1, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic"})
+            emit(line)
+        return
     if args.workload == "prefill":
         if rank == 0:
             line = prefill_leg(env, reps=max(1, min(args.steps, 5)))
@@ -970,7 +1098,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
     ap.add_argument("--model", default="8b", choices=["8b", "70b"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "nigenex"])
+    ap.add_argument("--sizes", default="2k,4k,4k-hd64", help="--workload nigenex: which of NIGENEX_SIZES to run")
     ap.add_argument("--extras", default="auto", choices=["auto", "none", "all"],
                     help="auto: config0 + config4 at N=1, config3 (70B) at N=8; none: the headline only")
     ap.add_argument("--e2e-steps", type=int, default=64)

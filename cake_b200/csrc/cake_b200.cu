@@ -24,6 +24,7 @@
 #include "attn_prefill.cuh"
 #include "attn_prefill_tc.cuh"
 #include "attn_window_bias.cuh"
+#include "attn_window_tc.cuh"
 #include "common.cuh"
 #include "decode_mega.cuh"
 #include "f32_stream.cuh"
@@ -352,7 +353,9 @@ template <typename T> static int set_smem_attrs_T() {
   CU(cudaFuncSetAttribute(gemm_tc_kernel<T, EPI, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<128>::SMEM_BYTES));      \
   CU(cudaFuncSetAttribute(gemm_tc_kernel<T, EPI, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<256>::SMEM_BYTES));      \
   CU(cudaFuncSetAttribute(gemm_tc_kernel<T, EPI, 256, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<256>::SMEM_BYTES));
-  SETT(TCE_PLAIN) SETT(TCE_RESIDUAL) SETT(TCE_SWIGLU) SETT(TCE_RESIDUAL_F32)
+  SETT(TCE_PLAIN) SETT(TCE_RESIDUAL) SETT(TCE_SWIGLU) SETT(TCE_RESIDUAL_F32) SETT(TCE_SOFTCAP_F32)
+  CU(cudaFuncSetAttribute(attn_window_tc_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, FT_SMEM_BYTES));
+  CU(cudaFuncSetAttribute(attn_window_tc_kernel<T>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
 #define SETW(HD) CU(cudaFuncSetAttribute(attn_window_mma_kernel<T, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, wm_smem_bytes<HD>()));
   SETW(32) SETW(64) SETW(96) SETW(128)
 #undef SETW
@@ -1128,7 +1131,7 @@ static bool tc_gemm_ok(int M, int N, int K) { return M >= 1 && N % TC_BN == 0 &&
 // C = epi(A[M,K] W[N,K]^T) on the tensor cores (gemm_tc.cuh)
 template <typename T, int EPI>
 static int gemm_tc_T(cake_b200_ctx *c, const void *A, const void *W, const void *bias, const void *res, void *C, int M, int N, int K,
-                     int act = -1, int ldc = 0) {
+                     int act = -1, int ldc = 0, float cap = 0.f) {
   // 128 x 256 tiles when N allows and there are enough tiles to fill the chip; CAKE_B200_TC_BN=128 forces the small tile (A/B aid)
   static const int force_bn = []() { const char *e = getenv("CAKE_B200_TC_BN"); return e ? atoi(e) : 0; }();
   const int tiles_m = (M + TC_BM - 1) / TC_BM;
@@ -1140,7 +1143,7 @@ static int gemm_tc_T(cake_b200_ctx *c, const void *A, const void *W, const void 
   CUtensorMap ma, mb;
   RC(make_tmap(&ma, A, (uint64_t)M, (uint64_t)K, c->cfg.dtype, TC_BM));
   RC(make_tmap(&mb, W, (uint64_t)N, (uint64_t)K, c->cfg.dtype, mc ? 128u : (uint32_t)bn));
-  TcParams p{bias, res, C, M, N, K, act >= 0 ? act : (c->cfg.use_gelu_mlp ? 1 : 0), ldc};
+  TcParams p{bias, res, C, M, N, K, act >= 0 ? act : (c->cfg.use_gelu_mlp ? 1 : 0), ldc, cap};
   const int tiles = tiles_m * (N / bn);
   dim3 grid(tiles < c->sm_count ? tiles : c->sm_count), block(TC_THREADS);
   if (mc) {
@@ -1325,7 +1328,7 @@ extern "C" int cake_b200_block_load_spec(cake_b200_ctx *c, int layer_idx, const 
   const int rc = [&]() -> int {
     // one input projection: rows cat(q, k, gate); padded with zero rows to the tensor-core tile so that it can take the shape
     b->n_in = (int)(sq + skv + (t->gate ? sp->heads : 0));
-    b->n_in_pad = round_up(b->n_in, TC_BN);
+    b->n_in_pad = round_up(b->n_in, b->n_in > 1024 ? 256 : TC_BN);  // wide projections take the 128 x 256 tile
     b->gate_col = t->gate ? (int)(sq + skv) : -1;
     CU(cudaMalloc(&b->w_in, (size_t)b->n_in_pad * H * es + 16));
     CU(cudaMemsetAsync(b->w_in, 0, (size_t)b->n_in_pad * H * es, 0));
@@ -1401,12 +1404,13 @@ template <typename T> static bool listed_tc(cake_b200_ctx *, int M, int N, int K
 }
 template <> bool listed_tc<float>(cake_b200_ctx *, int, int, int) { return false; }
 template <typename T, int EPI>
-static int listed_gemm_tc(cake_b200_ctx *c, const void *A, const void *W, const void *res, void *C, int M, int N, int K, int act, int ldc) {
-  return gemm_tc_T<T, EPI>(c, A, W, nullptr, res, C, M, N, K, act, ldc);
+static int listed_gemm_tc(cake_b200_ctx *c, const void *A, const void *W, const void *res, void *C, int M, int N, int K, int act, int ldc,
+                          float cap = 0.f) {
+  return gemm_tc_T<T, EPI>(c, A, W, nullptr, res, C, M, N, K, act, ldc, cap);
 }
-template <> int listed_gemm_tc<float, TCE_PLAIN>(cake_b200_ctx *, const void *, const void *, const void *, void *, int, int, int, int, int) { return CAKE_B200_EINVAL; }
-template <> int listed_gemm_tc<float, TCE_SWIGLU>(cake_b200_ctx *, const void *, const void *, const void *, void *, int, int, int, int, int) { return CAKE_B200_EINVAL; }
-template <> int listed_gemm_tc<float, TCE_RESIDUAL_F32>(cake_b200_ctx *, const void *, const void *, const void *, void *, int, int, int, int, int) { return CAKE_B200_EINVAL; }
+#define NO_TC_F32(EPI) template <> int listed_gemm_tc<float, EPI>(cake_b200_ctx *, const void *, const void *, const void *, void *, int, int, int, int, int, float) { return CAKE_B200_EINVAL; }
+NO_TC_F32(TCE_PLAIN) NO_TC_F32(TCE_SWIGLU) NO_TC_F32(TCE_RESIDUAL_F32) NO_TC_F32(TCE_SOFTCAP_F32)
+#undef NO_TC_F32
 
 // attention of a layer-list block: tensor cores for prompt portions in 16-bit D, the warp-split kernel for steps of a few
 // tokens, the warp-per-row kernel for everything else (any head_dim, D = float)
@@ -1423,11 +1427,27 @@ template <typename T> static int listed_attention_mma(cake_b200_ctx *c, const Wi
   return CAKE_B200_OK;
 }
 template <> int listed_attention_mma<float>(cake_b200_ctx *, const WinAttn &, bool *done) { *done = false; return CAKE_B200_OK; }
+// head_dim 128: the tcgen05 kernel (attn_window_tc.cuh); CAKE_B200_FA=mma keeps the mma.sync kernel (A/B aid)
+template <typename T> static int listed_attention_tc(cake_b200_ctx *c, const WinAttn &wa, bool *done) {
+  static const bool fa_mma = []() { const char *e = getenv("CAKE_B200_FA"); return e && !strcmp(e, "mma"); }();
+  static const float fa_tau = []() { const char *e = getenv("CAKE_B200_FA_TAU"); return e ? (float)atof(e) : 5.545f; }();
+  *done = false;
+  if (fa_mma || wa.hd != FT_HD || wa.ldy % 8 != 0 || wa.kc != wa.vc) return CAKE_B200_OK;
+  CUtensorMap mq, mk;
+  RC(make_tmap3(&mq, wa.qkg, (uint64_t)wa.ld, (uint64_t)wa.ld, (uint64_t)wa.S, (uint64_t)wa.S, (uint64_t)wa.B, c->cfg.dtype, FT_BM));
+  RC(make_tmap3(&mk, wa.kc, (uint64_t)wa.hd, (uint64_t)wa.hd, (uint64_t)(wa.pos0 + wa.S), (uint64_t)wa.cap, (uint64_t)wa.B * wa.n_kv, c->cfg.dtype, FT_BN));
+  dim3 gt((wa.S + FT_BM - 1) / FT_BM, wa.heads, wa.B);
+  *done = true;
+  return launch_pdl(c, attn_window_tc_kernel<T>, gt, dim3(FT_THREADS), (size_t)FT_SMEM_BYTES, mq, mk, mk, wa, fa_tau * 1.4426950408889634f);
+}
+template <> int listed_attention_tc<float>(cake_b200_ctx *, const WinAttn &, bool *done) { *done = false; return CAKE_B200_OK; }
 template <typename T> static int listed_attention(cake_b200_ctx *c, const WinAttn &wa) {
   static const bool no_mma = []() { const char *e = getenv("CAKE_B200_NO_TC"); return e && e[0] == '1'; }();
   const long items = (long)wa.B * wa.S * wa.heads;
   if (wa.S >= 16 && !no_mma && wa.ld % 8 == 0 && wa.ldy % 2 == 0) {
     bool done = false;
+    RC(listed_attention_tc<T>(c, wa, &done));
+    if (done) return CAKE_B200_OK;
     RC(listed_attention_mma<T>(c, wa, &done));
     if (done) return CAKE_B200_OK;
   }
@@ -1461,7 +1481,7 @@ static int enqueue_listed_layers(cake_b200_ctx *c, cake_b200_block *const *block
       // 1. h = norm(x) (for the feed-forward) and its token-shifted copy (for the mixer)
       const int cs = kc->shift_cur[l];
       const T *mix_in = (const T *)(b->shift ? c->sp_hs : c->sp_h);
-      RC(launch_pdl(c, norm_shift_rows_kernel<T>, dim3(M), dim3(256), 0, cur, (const int *)nullptr, (const T *)b->g, sp.scalar_norm ? 0 : 1,
+      RC(launch_pdl(c, norm_shift_rows_kernel<T>, dim3(M), dim3(256), 0, cur, (const int *)nullptr, 1, 0, (const T *)b->g, sp.scalar_norm ? 0 : 1,
                     (const T *)b->shift, (const float *)kc->shift_state[cs][l], kc->shift_state[cs ^ 1][l], (T *)c->sp_h, (T *)c->sp_hs, S, H,
                     c->cfg.rms_eps, pos0));
       // 2. q | k | gate logits in one product
@@ -1623,7 +1643,8 @@ extern "C" int cake_b200_embed(cake_b200_ctx *c, const uint32_t *ids_host, int b
 
 
 // fp32 logits of n rows of the fp32 stream: final norm (scalar or vector gain) -> lm_head -> soft cap
-static int listed_logits(cake_b200_ctx *c, const void *x_dev, const int *rows_host, int n, float *out_dev) {
+// rows_host == NULL: row i = i * row_mul + row_add (no table, nothing to wait for)
+static int listed_logits(cake_b200_ctx *c, const void *x_dev, const int *rows_host, int row_mul, int row_add, int n, float *out_dev) {
   const size_t H = c->cfg.hidden, V = c->cfg.vocab;
   if ((size_t)n > c->sp_logit_rows) {
     CU(cudaStreamSynchronize(c->stream));
@@ -1636,23 +1657,26 @@ static int listed_logits(cake_b200_ctx *c, const void *x_dev, const int *rows_ho
     CU(cudaMalloc(&c->sp_logits, (size_t)n * V * sizeof(float)));
     c->sp_logit_rows = n;
   }
-  CU(cudaMemcpyAsync(c->sp_rows_idx, rows_host, (size_t)n * sizeof(int), cudaMemcpyHostToDevice, c->stream));
-  CU(cudaStreamSynchronize(c->stream));  // rows_host is the caller's (pageable) memory
+  if (rows_host) {
+    CU(cudaMemcpyAsync(c->sp_rows_idx, rows_host, (size_t)n * sizeof(int), cudaMemcpyHostToDevice, c->stream));
+    CU(cudaStreamSynchronize(c->stream));  // rows_host is the caller's (pageable) memory
+  }
   return DISPATCH_T3(c->cfg.dtype, T_LAMBDA {
     typedef typename decltype(tag_)::type T;
-    RC(launch_pdl(c, norm_shift_rows_kernel<T>, dim3(n), dim3(256), 0, (const float *)x_dev, (const int *)c->sp_rows_idx, (const T *)c->ln_f,
+    RC(launch_pdl(c, norm_shift_rows_kernel<T>, dim3(n), dim3(256), 0, (const float *)x_dev, (const int *)(rows_host ? c->sp_rows_idx : nullptr),
+                  row_mul, row_add, (const T *)c->ln_f,
                   c->cfg.scalar_final_norm ? 0 : 1, (const T *)nullptr, (const float *)nullptr, (float *)nullptr, (T *)c->sp_hn, (T *)nullptr, 1,
                   (int)H, c->cfg.rms_eps, 0));
     RowsGemm g{c->sp_hn, c->lm_head, nullptr, out_dev ? out_dev : c->sp_logits, n, (int)V, (int)H, (int)H, (int)V, 0, c->cfg.logit_softcap};
+    if (listed_tc<T>(c, n, (int)V, (int)H))
+      return listed_gemm_tc<T, TCE_SOFTCAP_F32>(c, c->sp_hn, c->lm_head, nullptr, g.C, n, (int)V, (int)H, 0, 0, c->cfg.logit_softcap);
     return gemm_rows_T<T, RE_SOFTCAP_F32>(c, g);
   });
 }
 // cake_b200_logits for a layer-list model: the last position of every batch row; logits_dev receives them in the 16-bit
 // dtype the samplers read (bf16 when D is fp32)
 static int listed_logits_last(cake_b200_ctx *c, const void *x_dev, int batch, int seq, void *logits_dev, uint32_t *argmax_host) {
-  std::vector<int> rows(batch);
-  for (int b = 0; b < batch; b++) rows[b] = b * seq + seq - 1;
-  RC(listed_logits(c, x_dev, rows.data(), batch, nullptr));
+  RC(listed_logits(c, x_dev, nullptr, seq, seq - 1, batch, nullptr));
   const size_t V = c->cfg.vocab;
   if (!logits_dev && !argmax_host) return CAKE_B200_OK;
   return DISPATCH_T(c->cfg.dtype, T_LAMBDA {
@@ -1681,7 +1705,7 @@ extern "C" int cake_b200_logits_rows(cake_b200_ctx *c, const void *x_dev, int n_
     if (rows_host[i] < 0 || rows_host[i] >= n_rows_total) return fail(CAKE_B200_EINVAL, "row %d out of range (%d rows)", rows_host[i], n_rows_total);
   CU(cudaSetDevice(c->device));
   RC(wait_loads(c));
-  return listed_logits(c, x_dev, rows_host, n, logits_f32_dev);
+  return listed_logits(c, x_dev, rows_host, 1, 0, n, logits_f32_dev);
 }
 
 extern "C" int cake_b200_logits(cake_b200_ctx *c, const void *x_dev, int batch, int seq, void *logits_dev,

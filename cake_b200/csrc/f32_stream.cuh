@@ -46,8 +46,16 @@ __global__ void embed_f32_kernel(const T *__restrict__ E, const uint32_t *__rest
 //   t == 0, pos0 > 0 state_in[b] — the last h of the previous call, kept in fp32
 //   t == 0, pos0 == 0 zeros
 // The last row of every b leaves its h in state_out[b] (a different buffer than state_in: other CTAs still read that).
+template <typename T> __device__ __forceinline__ void store4(T *dst, float a, float b, float c, float d) {
+  *reinterpret_cast<uint2 *>(dst) = make_uint2(pack2x<T>(a, b), pack2x<T>(c, d));
+}
+template <> __device__ __forceinline__ void store4<float>(float *dst, float a, float b, float c, float d) {
+  *reinterpret_cast<float4 *>(dst) = make_float4(a, b, c, d);
+}
+
+// Source row of output row r: rows ? rows[r] : r * row_mul + row_add (the last position of every batch row needs no table).
 template <typename T>
-__global__ void __launch_bounds__(256) norm_shift_rows_kernel(const float *__restrict__ x, const int *__restrict__ rows,
+__global__ void __launch_bounds__(256) norm_shift_rows_kernel(const float *__restrict__ x, const int *__restrict__ rows, int row_mul, int row_add,
                                                               const T *__restrict__ g, int g_stride,
                                                               const T *__restrict__ shift, const float *__restrict__ state_in,
                                                               float *__restrict__ state_out, T *__restrict__ h_out,
@@ -56,19 +64,32 @@ __global__ void __launch_bounds__(256) norm_shift_rows_kernel(const float *__res
   pdl_wait();
   __shared__ float red[2][8];
   const int r = blockIdx.x;
-  const size_t src = rows ? (size_t)rows[r] : (size_t)r;
+  const size_t src = rows ? (size_t)rows[r] : (size_t)r * row_mul + row_add;
   const float *xr = x + src * n;
   const bool shifted = shift != nullptr;
   const int t = shifted ? r % S : 0, b = shifted ? r / S : 0;
   const bool prev_row = shifted && t > 0;
   const float *xp = xr - n;
+  const bool vec = (n & 3) == 0;   // rows of 16-byte multiples: 16-byte loads, 8- / 16-byte stores
   float ss = 0.f, sp = 0.f;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const float v = xr[i];
-    ss = fmaf(v, v, ss);
-    if (prev_row) {
-      const float u = xp[i];
-      sp = fmaf(u, u, sp);
+  if (vec) {
+    const float4 *x4 = reinterpret_cast<const float4 *>(xr), *p4 = reinterpret_cast<const float4 *>(xp);
+    for (int i = threadIdx.x; i < n / 4; i += blockDim.x) {
+      const float4 v = x4[i];
+      ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+      if (prev_row) {
+        const float4 u = p4[i];
+        sp = fmaf(u.x, u.x, sp); sp = fmaf(u.y, u.y, sp); sp = fmaf(u.z, u.z, sp); sp = fmaf(u.w, u.w, sp);
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      const float v = xr[i];
+      ss = fmaf(v, v, ss);
+      if (prev_row) {
+        const float u = xp[i];
+        sp = fmaf(u, u, sp);
+      }
     }
   }
   ss = warp_sum(ss);
@@ -81,6 +102,34 @@ __global__ void __launch_bounds__(256) norm_shift_rows_kernel(const float *__res
   const float invp = 1.0f / sqrtf(totp / (float)n + eps);
   const bool from_state = shifted && t == 0 && pos0 > 0;
   const bool last = shifted && t == S - 1;
+  if (vec) {  // the second read of the row comes out of L1 / L2
+    const float4 *x4 = reinterpret_cast<const float4 *>(xr), *p4 = reinterpret_cast<const float4 *>(xp);
+    const float4 *s4 = reinterpret_cast<const float4 *>(state_in + (from_state ? (size_t)b * n : 0));
+    for (int i = threadIdx.x; i < n / 4; i += blockDim.x) {
+      const float4 v = x4[i];
+      float gi[4], h[4];
+#pragma unroll
+      for (int e = 0; e < 4; e++) gi[e] = DT<T>::to_f(g[(size_t)(4 * i + e) * g_stride]);
+      h[0] = v.x * inv * gi[0]; h[1] = v.y * inv * gi[1]; h[2] = v.z * inv * gi[2]; h[3] = v.w * inv * gi[3];
+      if (h_out) store4<T>(h_out + (size_t)r * n + 4 * i, h[0], h[1], h[2], h[3]);
+      if (shifted) {
+        float hp[4] = {0.f, 0.f, 0.f, 0.f};
+        if (prev_row) {
+          const float4 u = p4[i];
+          hp[0] = u.x * invp * gi[0]; hp[1] = u.y * invp * gi[1]; hp[2] = u.z * invp * gi[2]; hp[3] = u.w * invp * gi[3];
+        } else if (from_state) {
+          const float4 u = s4[i];
+          hp[0] = u.x; hp[1] = u.y; hp[2] = u.z; hp[3] = u.w;
+        }
+        float o[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) o[e] = h[e] + (hp[e] - h[e]) * DT<T>::to_f(shift[4 * i + e]);
+        store4<T>(hs_out + (size_t)r * n + 4 * i, o[0], o[1], o[2], o[3]);
+        if (last) *reinterpret_cast<float4 *>(state_out + (size_t)b * n + 4 * i) = make_float4(h[0], h[1], h[2], h[3]);
+      }
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
     const float gi = DT<T>::to_f(g[(size_t)i * g_stride]);
     const float h = xr[i] * inv * gi;

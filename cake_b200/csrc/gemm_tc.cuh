@@ -37,7 +37,8 @@ template <int BN> struct TcCfg {
 constexpr int TC_SMEM_BYTES = TcCfg<256>::SMEM_BYTES > TcCfg<128>::SMEM_BYTES ? TcCfg<256>::SMEM_BYTES : TcCfg<128>::SMEM_BYTES;
 // TCE_RESIDUAL_F32: C (fp32) = residual (fp32) + accumulator, nothing rounded to D — the output projection of a block whose
 // residual stream is fp32 (f32_stream.cuh)
-enum { TCE_PLAIN = 0, TCE_RESIDUAL = 1, TCE_SWIGLU = 2, TCE_RESIDUAL_F32 = 3 };
+// TCE_SOFTCAP_F32: C (fp32) = cap * tanh(accumulator / cap) (cap == 0: the accumulator itself) — fp32 logits of such a model
+enum { TCE_PLAIN = 0, TCE_RESIDUAL = 1, TCE_SWIGLU = 2, TCE_RESIDUAL_F32 = 3, TCE_SOFTCAP_F32 = 4 };
 
 struct TcParams {
   const void *bias;      // [N] D or nullptr (TCE_PLAIN)
@@ -47,6 +48,7 @@ struct TcParams {
   int act;  // TCE_SWIGLU: 0 silu, 1 gelu_tanh
   int ldc;  // TCE_SWIGLU: row stride of C in elements when it is a column range of a wider buffer (0 = N/2; a multiple of 8,
             // like the column offset folded into C)
+  float cap; // TCE_SOFTCAP_F32
 };
 
 // Tile rasterisation: groups of TC_GM m-tiles (16 x 128 rows = 16 MB of A at K=4096) are walked n-major, so the A
@@ -266,6 +268,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             uint4 *dst = reinterpret_cast<uint4 *>(C + (size_t)row * (p.ldc ? p.ldc : p.N / 2) + (n0 + c0) / 2);
             dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
             dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+          } else if (EPI == TCE_SOFTCAP_F32) {
+            float4 *dst = reinterpret_cast<float4 *>(reinterpret_cast<float *>(p.C) + (size_t)row * p.N + n0 + c0);
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+              float v[4];
+#pragma unroll
+              for (int e = 0; e < 4; e++) {
+                const float a = __uint_as_float(r[4 * j + e]);
+                v[e] = p.cap > 0.f ? p.cap * tanhf(a / p.cap) : a;
+              }
+              dst[j] = make_float4(v[0], v[1], v[2], v[3]);
+            }
           } else if (EPI == TCE_RESIDUAL_F32) {
             const size_t off = (size_t)row * p.N + n0 + c0;
             const float4 *r4 = reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p.residual) + off);

@@ -166,6 +166,10 @@ struct Config {
     std::string txt = slurp(path);
     Json j = JsonParser(txt.data(), txt.size()).value();
     Config k;
+    if (const Json *one = j.get("architecture"))  // a layer-list model names itself with a single string and lists its layers
+      if (one->kind == Json::Str)
+        throw Error("architecture " + one->str + " is a layer-list model (per-layer sizes, fp32 residual stream): it is loaded by the "
+                    "Python host, `python -m cake_b200.run <model_dir> --prompt-ids ...`");
     if (const Json *a = j.get("architectures"))  // config.rs:175-190: the first *string* entry
       for (auto &e : a->arr)
         if (e.kind == Json::Str) { k.arch = e.str; break; }

@@ -280,6 +280,37 @@ def test_window_edges_with_a_dominant_key(mode):
 
 
 @gpu
+@pytest.mark.parametrize("hd", [128, 64, 96])
+def test_window_edges_on_tensor_core_shapes(hd):
+    """The same rig in bf16 at sizes the tensor-core kernels take (tcgen05 attention for head size 128, mma.sync for 64 and
+    96; tcgen05 GEMMs for width 128): prompt in one step, in portions around the window's size, and decoded."""
+    w = 70
+    layers = [LayerSpec(heads=2, kv_heads=2, head_dim=hd, window=w, scale=0.3, softcap=20.0, ff=0),
+              LayerSpec(heads=2, kv_heads=2, head_dim=hd, window=0, scale=0.3, softcap=20.0, ff=128)]
+    cfg = small_config(layers, width=128, vocab=128, logit_softcap=0.0)
+    sd = make_listed_checkpoint(cfg, "bf16", seed=18, std=0.12)
+    _spike(cfg, sd, 0, 7, gain=4.0)
+    _spike(cfg, sd, 1, 7, gain=1.0)
+    rng = np.random.default_rng(6)
+    toks = [int(t) for t in rng.integers(8, 128, 420)]
+    j = 150
+    toks[j] = 7
+    want = plain(cfg, sd, toks, "bf16")
+    assert np.abs(want[j + w - 1] - want[j + w]).max() > 20 * TOL["bf16"] * want.std()
+    r = Runner(cfg, sd, "bf16")
+    try:
+        runs = {"prompt": r.run("a", toks), "portions": r.run("b", toks, [w - 1, 2, w, w + 1, 129, 16]),
+                "decode": np.concatenate([r.run("c", toks[:j + 3], end=False), r.run("c", toks[j + 3:j + w + 40], [1])], 0)}
+        for mode, got in runs.items():
+            n = got.shape[0]
+            for p in (0, 1, j, j + 1, j + w - 2, j + w - 1, j + w, j + w + 1, n - 1):
+                assert rel_err(got[p], want[p]) < TOL["bf16"], (mode, p)
+            assert rel_err(got, want[:n]) < TOL["bf16"], mode
+    finally:
+        r.close()
+
+
+@gpu
 def test_interleaved_requests_and_reused_caches():
     """Two unequal requests stepped in turn equal each one alone; a cache given back by a finished request and taken by the
     next (longer and shorter than its predecessor) leaves no trace of the old rows or of the old shift state."""
