@@ -279,18 +279,18 @@ __global__ void __launch_bounds__(WM_THREADS, 2) attn_window_mma_kernel(const Wi
       }
     }
     float mx[2] = {-INFINITY, -INFINITY};
+    const float fq0 = (float)(qpos0 - j * WM_BN - c2);   // distance of this thread's first row to its first key of the tile
+    const float fwin = p.window > 0 ? (float)p.window : 3.0e38f;
 #pragma unroll
     for (int nt = 0; nt < NT; nt++)
 #pragma unroll
       for (int e = 0; e < 4; e++) {
-        const int key = j * WM_BN + nt * 8 + c2 + (e & 1);
-        const int d = qpos0 + (e >> 1) * 8 - key;
-        float v = -INFINITY;
-        if (d >= 0 && (p.window == 0 || d < p.window)) {
-          v = s[nt][e] * p.scale;
-          if (p.softcap > 0.f) v = p.softcap * (1.0f - __fdividef(2.0f, __expf(v * inv_cap2) + 1.0f));
-          if (biased) v -= r1 * __logf(1.0f + r2 * (float)d);
-        }
+        // branch-free (the independent chains interleave); the distance as a float: no I2F on the MUFU pipe
+        const float fd = fq0 + (float)((e >> 1) * 8 - nt * 8 - (e & 1));
+        float v = s[nt][e] * p.scale;
+        if (p.softcap > 0.f) v = p.softcap * (1.0f - __fdividef(2.0f, __expf(v * inv_cap2) + 1.0f));
+        if (biased) v -= r1 * __logf(fmaf(r2, fmaxf(fd, 0.f), 1.0f));
+        v = (fd >= 0.f && fd < fwin) ? v : -INFINITY;
         s[nt][e] = v;
         mx[e >> 1] = fmaxf(mx[e >> 1], v);
       }

@@ -145,17 +145,19 @@ attn_window_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         for (int i = 0; i < 32; i++) sv[32 + i] = __uint_as_float(r[i]);
       }
       // soft cap, distance bias, window: every score of the tile (the transcendentals dominate, a tile-level test would not pay)
+      // Branch-free, so that the 64 independent chains of a row interleave (MUFU latency is what a softmax warp waits for):
+      // the distance is carried as a float (exact below 2^24, no I2F on the MUFU pipe), masked entries take the arithmetic
+      // with a clamped distance and are replaced by -inf at the end.
       float mx = -INFINITY;
-      const int d0 = qp - (j_lo + j) * FT_BN;  // distance to the tile's first key
+      const float fd0 = (float)(qp - (j_lo + j) * FT_BN);  // distance to the tile's first key
+      const float fwin = p.window > 0 ? (float)p.window : 3.0e38f;
 #pragma unroll
       for (int i = 0; i < FT_BN; i++) {
-        const int d = d0 - i;
-        float v = -INFINITY;
-        if (d >= 0 && (p.window == 0 || d < p.window)) {
-          v = sv[i] * p.scale;
-          if (p.softcap > 0.f) v = p.softcap * (1.0f - __fdividef(2.0f, __expf(v * inv_cap2) + 1.0f));
-          if (biased) v -= r1 * __logf(1.0f + r2 * (float)d);
-        }
+        const float fd = fd0 - (float)i;
+        float v = sv[i] * p.scale;
+        if (p.softcap > 0.f) v = p.softcap * (1.0f - __fdividef(2.0f, __expf(v * inv_cap2) + 1.0f));
+        if (biased) v -= r1 * __logf(fmaf(r2, fmaxf(fd, 0.f), 1.0f));
+        v = (fd >= 0.f && fd < fwin) ? v : -INFINITY;
         sv[i] = v;
         mx = fmaxf(mx, v);
       }
