@@ -142,9 +142,9 @@ __global__ void __launch_bounds__(128) attn_window_bias_kernel(const WinAttn p) 
   }
 }
 
-// Single-token steps: one CTA per (token, head); its 8 warps take the window's 32-key tiles in turn and merge their
+// Single-token steps: one CTA per (token, head); its 16 warps take the window's 32-key tiles in turn and merge their
 // (m, l, acc) states in shared memory in warp order, so the result does not depend on timing.
-constexpr int WA_DEC_WARPS = 8;
+constexpr int WA_DEC_WARPS = 16;
 template <typename T>
 __global__ void __launch_bounds__(WA_DEC_WARPS * 32) attn_window_decode_kernel(const WinAttn p) {
   pdl_launch_dependents();

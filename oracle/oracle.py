@@ -19,8 +19,13 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _SO = os.path.join(_HERE, "_build", "libcake_oracle.so")
 
 
+# ora_config mirrors the Llama-family prefix of cake_b200_config; the layer-list fields behind it have their own oracle
+# (oracle/nigenex_plain.py)
+_ORA_FIELDS = [f for f in CConfig._fields_ if f[0] not in ("layer_list", "logit_softcap", "scalar_final_norm")]
+
+
 class OraConfig(ctypes.Structure):
-    _fields_ = list(CConfig._fields_) + [("silu_mode", ctypes.c_int)]
+    _fields_ = list(_ORA_FIELDS) + [("silu_mode", ctypes.c_int)]
 
 
 class OraLayer(ctypes.Structure):
@@ -210,7 +215,7 @@ class OracleModel:
                  silu_mode: int = 0, layers: Optional[range] = None):
         self.cfg, self.dtype = cfg, dtype
         cc = CConfig.from_config(cfg, dtype, max_seq)
-        self.ccfg = OraConfig(*[getattr(cc, f) for f, _ in CConfig._fields_], silu_mode)
+        self.ccfg = OraConfig(*[getattr(cc, f) for f, _ in _ORA_FIELDS], silu_mode)
         self.h = lib().ora_model_create(ctypes.byref(self.ccfg))
         self._keep = []
         p = cfg.model_prefix

@@ -17,9 +17,28 @@ pub struct cake_b200_config {
     pub rms_eps: f32, pub rope_theta: f32, pub partial_rotary: f32,
     pub qkv_bias: c_int, pub qk_norm: c_int, pub tie_embeddings: c_int,
     pub rope_llama3: c_int, pub rope_factor: f32, pub rope_low: f32, pub rope_high: f32, pub rope_orig_max: c_int,
-    pub dtype: c_int, // 0 = bf16, 1 = f16
+    pub dtype: c_int, // 0 = bf16, 1 = f16, 2 = f32 (layer-list models only)
     pub sliding_window: c_int, pub use_gelu_mlp: c_int, pub embed_scale: f32,
     pub pre_reshape_qk_norm: c_int, // config.rs:116 (OLMo2)
+    // layer-list models (per-layer geometry, fp32 residual stream): not a reference architecture, zero for cake's own models
+    pub layer_list: c_int, pub logit_softcap: f32, pub scalar_final_norm: c_int,
+}
+
+/// `cake_b200_layer_spec` / `cake_b200_layer_tensors` (include/cake_b200.h): one layer of a layer-list model.
+#[repr(C)]
+#[derive(Clone, Copy, Debug)]
+pub struct cake_b200_layer_spec {
+    pub heads: c_int, pub kv_heads: c_int, pub head_dim: c_int, pub window: c_int,
+    pub scale: f32, pub softcap: f32,
+    pub values_are_keys: c_int, pub ff: c_int, pub act: c_int, pub scalar_norm: c_int,
+}
+#[repr(C)]
+#[derive(Clone, Copy, Debug)]
+pub struct cake_b200_layer_tensors {
+    pub norm: *const c_void, pub shift: *const c_void,
+    pub q: *const c_void, pub k: *const c_void, pub v: *const c_void, pub o: *const c_void,
+    pub r1: *const c_void, pub r2: *const c_void, pub gate: *const c_void,
+    pub ff_gate: *const c_void, pub ff_up: *const c_void, pub ff_down: *const c_void,
 }
 
 #[link(name = "cake_b200")]
@@ -81,6 +100,10 @@ extern "C" {
     pub fn cake_b200_decode_set_sampling(ctx: *mut cake_b200_ctx, sampling: *const cake_b200_sampling) -> c_int;
     pub fn cake_b200_load_stats(ctx: *mut cake_b200_ctx, bytes: *mut f64, seconds: *mut f64) -> c_int;
     pub fn cake_b200_block_set_variant(block: *mut cake_b200_block, variant: *const cake_b200_block_variant) -> c_int;
+    pub fn cake_b200_block_load_spec(ctx: *mut cake_b200_ctx, layer_idx: c_int, spec: *const cake_b200_layer_spec,
+        tensors: *const cake_b200_layer_tensors, out: *mut *mut cake_b200_block) -> c_int;
+    pub fn cake_b200_logits_rows(ctx: *mut cake_b200_ctx, x_dev: *const c_void, n_rows_total: c_int, rows_host: *const c_int, n: c_int,
+        logits_f32_dev: *mut f32) -> c_int;
 }
 
 /// `cake_b200_block_variant` (include/cake_b200.h): norm placement and per-layer attention mode of the OLMo2 / Gemma3 /

@@ -30,6 +30,7 @@ class CpuContext:
         self._children = []
         capi.check(capi.lib().cake_b200_ctx_create(device, ctypes.byref(self.ccfg), ctypes.byref(self.h)))
         self.torch_dtype = TORCH_DTYPES[dtype]
+        self.stream_dtype = self.logits_dtype = self.torch_dtype
         self.torch_stream = None
         self.cache = Cache(self)
 
@@ -39,8 +40,8 @@ class CpuContext:
     def launch_count(self):
         return 0
 
-    def empty(self, *shape):
-        return torch.empty(shape, dtype=self.torch_dtype)
+    def empty(self, *shape, dtype=None):
+        return torch.empty(shape, dtype=dtype or self.torch_dtype)
 
     def to_device(self, t):
         return t.to(self.torch_dtype).contiguous().clone()

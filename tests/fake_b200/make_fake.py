@@ -139,7 +139,7 @@ int cake_b200_ctx_create(int device, const cake_b200_config *cfg, cake_b200_ctx 
   if (!cfg || !out) return fail(CAKE_B200_EINVAL, "null argument");
   cake_b200_ctx *c = (cake_b200_ctx *)calloc(1, sizeof *c);
   c->cfg = *cfg;
-  memcpy(&c->oc, cfg, sizeof *cfg);
+  memcpy(&c->oc, cfg, offsetof(cake_b200_config, layer_list));  /* ora_config = the Llama-family prefix + silu_mode */
   c->oc.silu_mode = 0;
   c->m = ora_model_create(&c->oc);
   *out = c; (void)device;
