@@ -296,6 +296,8 @@ def listed_block_tensors(vb, cfg: Config, index: int) -> Dict[str, Optional[torc
         t = vb.get(f"{name}.{short}")
         if t is None:
             raise KeyError(f"tensor {name}.{short} not found")
+        if fld == "norm" and t.numel() == 1:
+            t = t.reshape(())          # a one-number gain may be stored as [] or [1]
         if tuple(t.shape) != tuple(shapes[fld]):
             raise ValueError(f"shape mismatch for {name}.{short}, expected: {list(shapes[fld])}, got: {list(t.shape)}")
         out[fld] = t

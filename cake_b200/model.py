@@ -317,6 +317,8 @@ class TextModelBase:
         block_cls = block_cls or BLOCK_CLASSES.get(cfg.block_kind, B200Transformer)
         def get(tname: str, shape):
             t = vb[tname]
+            if shape == () and t.numel() == 1:
+                t = t.reshape(())      # a one-number gain may be stored as [] or [1]
             if tuple(t.shape) != tuple(shape):
                 raise ValueError(f"shape mismatch for {tname}, expected: {list(shape)}, got: {list(t.shape)}")
             return t.to(ctx.torch_dtype).contiguous()

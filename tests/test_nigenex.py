@@ -357,11 +357,11 @@ def test_long_decode_past_every_window():
 @pytest.mark.parametrize("dtype", ["f32", "bf16"])
 def test_other_sizes(dtype):
     """Sizes that exercise the tensor-core shapes (width and ff multiples of 64, head sizes 64 and 128) and ones that do not
-    (odd width, head size 20), heads == kv_heads and one kv head, ff != width, a window longer than the sequence."""
+    (width 42, head size 20, ff 101), heads == kv_heads and one kv head, ff != width, a window longer than the sequence."""
     for seed, (width, layers) in enumerate([
         (128, [LayerSpec(heads=4, kv_heads=1, head_dim=64, window=50, scale=0.125, softcap=30.0, ff=256),
                LayerSpec(heads=2, kv_heads=2, head_dim=128, window=4000, scale=0.09, softcap=15.0, ff=128)]),
-        (40, [LayerSpec(heads=5, kv_heads=5, head_dim=20, window=3, scale=0.2, softcap=8.0, ff=100)]),
+        (42, [LayerSpec(heads=5, kv_heads=5, head_dim=20, window=3, scale=0.2, softcap=8.0, ff=101)]),   # rows that are no multiple of 16 bytes
         (192, [LayerSpec(heads=8, kv_heads=2, head_dim=96, window=64, scale=0.1, softcap=25.0, ff=320)] * 2),
     ]):
         cfg = small_config(layers, width=width, vocab=130)
