@@ -22,6 +22,8 @@ template <> struct DT<float> {
 };
 
 // ---- embedding gather into the fp32 stream ------------------------------------------------------------------------------
+template <typename T> struct EmbedBits { typedef T type; };
+template <> struct EmbedBits<float> { typedef __nv_bfloat16 type; };  // never taken for float (sizeof test); keeps unpack8 instantiable
 template <typename T>
 __global__ void embed_f32_kernel(const T *__restrict__ E, const uint32_t *__restrict__ ids, float *__restrict__ x, int n_tok,
                                  int H, int vocab, float scale /* 0 = none */) {
@@ -33,6 +35,17 @@ __global__ void embed_f32_kernel(const T *__restrict__ E, const uint32_t *__rest
   if (id >= (uint32_t)vocab) id = 0;
   const T *src = E + (size_t)id * H;
   float *dst = x + (size_t)t * H;
+  if (sizeof(T) == 2 && (H & 7) == 0 && scale == 0.f) {  // 16-byte loads, two 16-byte stores per thread and step
+    const uint4 *s4 = reinterpret_cast<const uint4 *>(src);
+    float4 *d4 = reinterpret_cast<float4 *>(dst);
+    for (int i = threadIdx.x; i < H / 8; i += blockDim.x) {
+      float f[8];
+      unpack8<typename EmbedBits<T>::type>(s4[i], f);
+      d4[2 * i] = make_float4(f[0], f[1], f[2], f[3]);
+      d4[2 * i + 1] = make_float4(f[4], f[5], f[6], f[7]);
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
     const float v = DT<T>::to_f(src[i]);
     dst[i] = scale == 0.f ? v : v * scale;
@@ -217,6 +230,15 @@ __global__ void rows_to_cache_kernel(const T *__restrict__ src, T *__restrict__ 
   pdl_wait();
   const int r = blockIdx.x, b = r / S, t = r % S;
   const T *s = src + (size_t)r * ld + col0;
+  constexpr int VE = 16 / (int)sizeof(T);  // elements per 16-byte copy
+  if (hd % VE == 0 && ld % VE == 0 && col0 % VE == 0) {
+    const int cpr = hd / VE;  // 16-byte chunks per head row
+    for (int i = threadIdx.x; i < n_kv * cpr; i += blockDim.x) {
+      const int g = i / cpr, c = i % cpr;
+      reinterpret_cast<uint4 *>(cache + (((size_t)b * n_kv + g) * cap + pos0 + t) * hd)[c] = reinterpret_cast<const uint4 *>(s + (size_t)g * hd)[c];
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < n_kv * hd; i += blockDim.x) {
     const int g = i / hd, d = i % hd;
     cache[(((size_t)b * n_kv + g) * cap + pos0 + t) * hd + d] = s[i];

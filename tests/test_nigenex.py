@@ -107,7 +107,7 @@ def test_loader_checks_listed_shapes(tmp_path):
 
 
 def test_plain_mechanisms_alone():
-    """The checker's own pieces against hand-computed values."""
+    """The plain restatement's pieces against hand-computed values."""
     x = torch.tensor([[3.0, 4.0]])
     assert torch.allclose(P.rms_norm_scalar(x, 2.0, 0.0), x / (12.5 ** 0.5) * 2.0)
     h = torch.tensor([[1.0, 1.0], [3.0, 5.0]])
@@ -362,7 +362,7 @@ def test_other_sizes(dtype):
         (128, [LayerSpec(heads=4, kv_heads=1, head_dim=64, window=50, scale=0.125, softcap=30.0, ff=256),
                LayerSpec(heads=2, kv_heads=2, head_dim=128, window=4000, scale=0.09, softcap=15.0, ff=128)]),
         (42, [LayerSpec(heads=5, kv_heads=5, head_dim=20, window=3, scale=0.2, softcap=8.0, ff=101)]),   # rows that are no multiple of 16 bytes
-        (192, [LayerSpec(heads=8, kv_heads=2, head_dim=96, window=64, scale=0.1, softcap=25.0, ff=320)] * 2),
+        (192, [LayerSpec(heads=6, kv_heads=3, head_dim=96, window=64, scale=0.1, softcap=25.0, ff=320)] * 2),
     ]):
         cfg = small_config(layers, width=width, vocab=130)
         sd = make_listed_checkpoint(cfg, dtype, seed=30 + seed)
