@@ -15,6 +15,8 @@
 //                                one key of a 32-key tile, the tile's keys are then accumulated dimension-parallel
 //   attn_window_decode_kernel    one CTA per (token, head) for steps of a few tokens: its warps split the window and merge
 //                                their partial softmax states in shared memory
+//   attn_window_decode_vec_kernel the same for 16-bit D with rows of whole 16-byte pieces and values == keys: eight lanes
+//                                per key, the row read once for the score and the weighted sum
 //   attn_window_mma_kernel       prompt portions on the tensor cores for 16-bit D (below)
 // Nothing here follows a reference file: the reference has none of these modifiers.
 #pragma once
@@ -177,6 +179,125 @@ __global__ void __launch_bounds__(WA_DEC_WARPS * 32) attn_window_decode_kernel(c
   for (int i = 0; i < MAXD; i++) {
     const int d = lane + 32 * i;
     if (d < hd) sm_acc[warp][d] = acc[i];
+  }
+  __syncthreads();
+  float mx = -INFINITY;
+  for (int w = 0; w < WA_DEC_WARPS; w++) mx = fmaxf(mx, sm_m[w]);
+  float lt = 0.f;
+  for (int w = 0; w < WA_DEC_WARPS; w++) lt += sm_m[w] == -INFINITY ? 0.f : sm_l[w] * expf(sm_m[w] - mx);
+  float gate = 1.0f;
+  if (p.gate_col >= 0) gate = 1.0f / (1.0f + expf(-DT<T>::to_f(qrow[p.gate_col + h])));
+  const float inv = gate / lt;
+  T *yo = reinterpret_cast<T *>(p.y) + (size_t)(b * p.S + t) * p.ldy + h * hd;
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    float a = 0.f;
+    for (int w = 0; w < WA_DEC_WARPS; w++)
+      if (sm_m[w] != -INFINITY) a = fmaf(sm_acc[w][d], expf(sm_m[w] - mx), a);
+    yo[d] = DT<T>::from_f(a * inv);
+  }
+}
+
+// Single-token steps for 16-bit D, head_dim a multiple of 8, values == keys.  Eight lanes share a key: lane r of a group
+// holds the 16-byte pieces r, r + 8, ... of the row (NCH of them), so a warp's loads are whole rows, a score costs three
+// shuffles, and the registers that fed the dot product also feed the weighted sum (the key is read once).  Every group
+// keeps its own running (m, l, acc) over the keys lo + grp, lo + grp + 64, ... with U rows in flight; the groups merge in a
+// fixed order — shuffles inside a warp, shared memory across the warps — so the result does not depend on timing.
+template <typename T, int NCH>
+__global__ void __launch_bounds__(WA_DEC_WARPS * 32) attn_window_decode_vec_kernel(const WinAttn p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int NG = WA_DEC_WARPS * 4;  // key groups of a CTA
+  constexpr int U = NCH >= 3 ? 2 : 4;   // keys in flight per group
+  __shared__ float sm_m[WA_DEC_WARPS], sm_l[WA_DEC_WARPS];
+  __shared__ float sm_acc[WA_DEC_WARPS][WA_MAX_HD];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, grp = threadIdx.x >> 3, r = threadIdx.x & 7;
+  const int item = blockIdx.x;
+  const int h = item % p.heads, t = (item / p.heads) % p.S, b = item / (p.heads * p.S);
+  const int hd = p.hd, CH = hd >> 3, G = p.heads / p.n_kv;
+  const T *qrow = reinterpret_cast<const T *>(p.qkg) + (size_t)(b * p.S + t) * p.ld;
+  const T *kc = reinterpret_cast<const T *>(p.kc) + ((size_t)b * p.n_kv + h / G) * p.cap * hd;
+  float q[NCH][8], acc[NCH][8];
+#pragma unroll
+  for (int c = 0; c < NCH; c++) {
+    const int ch = r + 8 * c;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);  // sixteen zero bits are 0.0 in both 16-bit types
+    if (ch < CH) v = reinterpret_cast<const uint4 *>(qrow + (size_t)h * hd)[ch];
+    unpack8<T>(v, q[c]);
+#pragma unroll
+    for (int e = 0; e < 8; e++) acc[c][e] = 0.f;
+  }
+  const bool biased = p.r1 != nullptr;
+  const float r1 = biased ? DT<T>::to_f(reinterpret_cast<const T *>(p.r1)[h]) : 0.f;
+  const float r2 = biased ? DT<T>::to_f(reinterpret_cast<const T *>(p.r2)[h]) : 0.f;
+  const int pi = p.pos0 + t;
+  const int lo = p.window > 0 ? max(0, pi - p.window + 1) : 0;
+  float m = -INFINITY, l = 0.f;
+  for (int base = lo; base <= pi; base += NG * U) {  // the trip count is the same for every thread: the shuffles below are whole-warp
+    uint4 kr[U][NCH];
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const int j = base + u * NG + grp;
+#pragma unroll
+      for (int c = 0; c < NCH; c++) {
+        const int ch = r + 8 * c;
+        kr[u][c] = make_uint4(0u, 0u, 0u, 0u);
+        if (j <= pi && ch < CH) kr[u][c] = reinterpret_cast<const uint4 *>(kc + (size_t)j * hd)[ch];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const int j = base + u * NG + grp;
+      float kf[NCH][8];
+      float d = 0.f;
+#pragma unroll
+      for (int c = 0; c < NCH; c++) {
+        unpack8<T>(kr[u][c], kf[c]);
+#pragma unroll
+        for (int e = 0; e < 8; e++) d = fmaf(q[c][e], kf[c][e], d);
+      }
+      d += __shfl_xor_sync(0xffffffffu, d, 1);
+      d += __shfl_xor_sync(0xffffffffu, d, 2);
+      d += __shfl_xor_sync(0xffffffffu, d, 4);
+      if (j <= pi) {
+        const float s = wa_score(d, p, r1, r2, biased, pi, j);
+        const float mn = fmaxf(m, s);
+        const float f = (m == -INFINITY) ? 0.f : expf(m - mn);
+        const float w = expf(s - mn);
+        l = fmaf(l, f, w);
+        m = mn;
+#pragma unroll
+        for (int c = 0; c < NCH; c++)
+#pragma unroll
+          for (int e = 0; e < 8; e++) acc[c][e] = fmaf(acc[c][e], f, w * kf[c][e]);
+      }
+    }
+  }
+  // the four groups of a warp: common maximum, rescale, sum (a + b is the same number on both sides of an exchange)
+  float mw = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
+  mw = fmaxf(mw, __shfl_xor_sync(0xffffffffu, mw, 16));
+  const float sc = (m == -INFINITY) ? 0.f : expf(m - mw);
+  l *= sc;
+  l += __shfl_xor_sync(0xffffffffu, l, 8);
+  l += __shfl_xor_sync(0xffffffffu, l, 16);
+#pragma unroll
+  for (int c = 0; c < NCH; c++)
+#pragma unroll
+    for (int e = 0; e < 8; e++) {
+      float a = acc[c][e] * sc;
+      a += __shfl_xor_sync(0xffffffffu, a, 8);
+      a += __shfl_xor_sync(0xffffffffu, a, 16);
+      acc[c][e] = a;
+    }
+  if (lane == 0) { sm_m[warp] = mw; sm_l[warp] = l; }
+  if (lane < 8) {
+#pragma unroll
+    for (int c = 0; c < NCH; c++) {
+      const int ch = lane + 8 * c;
+      if (ch < CH) {
+#pragma unroll
+        for (int e = 0; e < 8; e++) sm_acc[warp][ch * 8 + e] = acc[c][e];
+      }
+    }
   }
   __syncthreads();
   float mx = -INFINITY;

@@ -1441,6 +1441,22 @@ template <typename T> static int listed_attention_tc(cake_b200_ctx *c, const Win
   return launch_pdl(c, attn_window_tc_kernel<T>, gt, dim3(FT_THREADS), (size_t)FT_SMEM_BYTES, mq, mk, mk, wa, fa_tau * 1.4426950408889634f);
 }
 template <> int listed_attention_tc<float>(cake_b200_ctx *, const WinAttn &, bool *done) { *done = false; return CAKE_B200_OK; }
+// steps of a few tokens in 16-bit D with 16-byte rows: eight lanes per key (attn_window_decode_vec_kernel)
+template <typename T> static int listed_attention_vec(cake_b200_ctx *c, const WinAttn &wa, bool *done) {
+  *done = false;
+  if (wa.hd % 8 != 0 || wa.hd > WA_MAX_HD || wa.ld % 8 != 0 || wa.kc != wa.vc || wa.gate_col < -1 ||
+      (((uintptr_t)wa.qkg | (uintptr_t)wa.kc) & 15) != 0)
+    return CAKE_B200_OK;
+  const dim3 grid((unsigned)((long)wa.B * wa.S * wa.heads)), block(WA_DEC_WARPS * 32);
+  *done = true;
+  switch ((wa.hd + 63) / 64) {
+    case 1: return launch_pdl(c, attn_window_decode_vec_kernel<T, 1>, grid, block, 0, wa);
+    case 2: return launch_pdl(c, attn_window_decode_vec_kernel<T, 2>, grid, block, 0, wa);
+    case 3: return launch_pdl(c, attn_window_decode_vec_kernel<T, 3>, grid, block, 0, wa);
+    default: return launch_pdl(c, attn_window_decode_vec_kernel<T, 4>, grid, block, 0, wa);
+  }
+}
+template <> int listed_attention_vec<float>(cake_b200_ctx *, const WinAttn &, bool *done) { *done = false; return CAKE_B200_OK; }
 template <typename T> static int listed_attention(cake_b200_ctx *c, const WinAttn &wa) {
   static const bool no_mma = []() { const char *e = getenv("CAKE_B200_NO_TC"); return e && e[0] == '1'; }();
   const long items = (long)wa.B * wa.S * wa.heads;
@@ -1449,6 +1465,11 @@ template <typename T> static int listed_attention(cake_b200_ctx *c, const WinAtt
     RC(listed_attention_tc<T>(c, wa, &done));
     if (done) return CAKE_B200_OK;
     RC(listed_attention_mma<T>(c, wa, &done));
+    if (done) return CAKE_B200_OK;
+  }
+  if (wa.S <= 8 && !no_mma) {
+    bool done = false;
+    RC(listed_attention_vec<T>(c, wa, &done));
     if (done) return CAKE_B200_OK;
   }
   if (wa.S <= 8) return launch_pdl(c, attn_window_decode_kernel<T>, dim3((unsigned)items), dim3(WA_DEC_WARPS * 32), 0, wa);

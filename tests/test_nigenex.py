@@ -280,10 +280,12 @@ def test_window_edges_with_a_dominant_key(mode):
 
 
 @gpu
-@pytest.mark.parametrize("hd", [128, 64, 96])
+@pytest.mark.parametrize("hd", [128, 64, 96, 160, 256, 24])
 def test_window_edges_on_tensor_core_shapes(hd):
     """The same rig in bf16 at sizes the tensor-core kernels take (tcgen05 attention for head size 128, mma.sync for 64 and
-    96; tcgen05 GEMMs for width 128): prompt in one step, in portions around the window's size, and decoded."""
+    96; tcgen05 GEMMs for width 128) and at head sizes they do not take: prompt in one step, in portions around the
+    window's size, and decoded (the eight-lanes-per-key kernel with one to four 16-byte pieces per lane; 24 = three pieces
+    per key, five lanes of a group idle)."""
     w = 70
     layers = [LayerSpec(heads=2, kv_heads=2, head_dim=hd, window=w, scale=0.3, softcap=20.0, ff=0),
               LayerSpec(heads=2, kv_heads=2, head_dim=hd, window=0, scale=0.3, softcap=20.0, ff=128)]
