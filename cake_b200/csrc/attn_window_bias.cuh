@@ -231,6 +231,7 @@ __global__ void __launch_bounds__(WA_DEC_WARPS * 32) attn_window_decode_vec_kern
   const float r2 = biased ? DT<T>::to_f(reinterpret_cast<const T *>(p.r2)[h]) : 0.f;
   const int pi = p.pos0 + t;
   const int lo = p.window > 0 ? max(0, pi - p.window + 1) : 0;
+  const float inv_cap2 = p.softcap > 0.f ? 2.0f / p.softcap : 0.f;
   float m = -INFINITY, l = 0.f;
   for (int base = lo; base <= pi; base += NG * U) {  // the trip count is the same for every thread: the shuffles below are whole-warp
     uint4 kr[U][NCH];
@@ -259,16 +260,25 @@ __global__ void __launch_bounds__(WA_DEC_WARPS * 32) attn_window_decode_vec_kern
       d += __shfl_xor_sync(0xffffffffu, d, 2);
       d += __shfl_xor_sync(0xffffffffu, d, 4);
       if (j <= pi) {
-        const float s = wa_score(d, p, r1, r2, biased, pi, j);
-        const float mn = fmaxf(m, s);
-        const float f = (m == -INFINITY) ? 0.f : expf(m - mn);
-        const float w = expf(s - mn);
-        l = fmaf(l, f, w);
-        m = mn;
+        // the modifiers as in the tensor-core kernels below (MUFU-based tanh and ln: |error| ~1e-6 of a score)
+        float s = d * p.scale;
+        if (p.softcap > 0.f) s = p.softcap * (1.0f - __fdividef(2.0f, __expf(s * inv_cap2) + 1.0f));
+        if (biased) s -= r1 * __logf(fmaf(r2, (float)(pi - j), 1.0f));
+        if (s > m) {  // a new maximum is rare after the first keys: rescale only then
+          const float f = (m == -INFINITY) ? 0.f : __expf(m - s);
+          l *= f;
+#pragma unroll
+          for (int c = 0; c < NCH; c++)
+#pragma unroll
+            for (int e = 0; e < 8; e++) acc[c][e] *= f;
+          m = s;
+        }
+        const float w = __expf(s - m);
+        l += w;
 #pragma unroll
         for (int c = 0; c < NCH; c++)
 #pragma unroll
-          for (int e = 0; e < 8; e++) acc[c][e] = fmaf(acc[c][e], f, w * kf[c][e]);
+          for (int e = 0; e < 8; e++) acc[c][e] = fmaf(w, kf[c][e], acc[c][e]);
       }
     }
   }
