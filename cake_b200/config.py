@@ -38,7 +38,7 @@ class LayerSpec:
     heads: int
     kv_heads: int
     head_dim: int
-    window: int = 0          # position i sees j with 0 <= i - j < window; 0 = all j <= i
+    window: int = 0          # row i attends to the keys j with i - window < j <= i; 0 = all j <= i
     scale: float = 1.0
     softcap: float = 0.0     # 0 = none
     ff: int = 0              # 0 = the layer has no feed-forward
@@ -175,7 +175,7 @@ class Config:
                 raise ValueError(f"layer {i}: mixer type {L.get('type')!r} is not part of this design")
             m = L["mixer"]
             if int(m.get("vdim", m["dim"])) != int(m["dim"]):
-                raise ValueError(f"layer {i}: the values are the keys, so vdim {m['vdim']} must equal dim {m['dim']}")
+                raise ValueError(f"layer {i}: the keys double as values, so vdim {m['vdim']} must equal dim {m['dim']}")
             mlp = L.get("mlp")
             if mlp is not None and mlp.get("kind") != "dense":
                 raise ValueError(f"layer {i}: feed-forward kind {mlp.get('kind')!r} is not part of this design")

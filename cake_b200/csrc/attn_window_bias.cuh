@@ -4,8 +4,8 @@
 //   s_ij = (q_i . k_j) * scale
 //   softcap > 0      s <- softcap * tanh(s / softcap)
 //   r1, r2 non-null  s <- s - r1[h] * ln(1 + r2[h] * (i - j))           (a bias that grows with the distance, per query head)
-//   window > 0       i sees j with 0 <= i - j < window; window == 0: every j <= i
-//   p = softmax over the visible j (fp32);   out_i = sum_j p_ij v_j   with v == k when the values are the keys (vc == kc)
+//   window > 0       row i attends to the keys j with i - window < j <= i; window == 0: every j <= i
+//   p = softmax over the visible j (fp32);   out_i = sum_j p_ij v_j   with v == k when the keys double as values (vc == kc)
 //   gate_col >= 0    out_i <- out_i * sigmoid(z_ih), z_ih = column gate_col + h of the projection row of token i
 //
 // Scores, bias, softmax and the weighted sum are fp32 whatever D is.  Keys are read only from the cache (the step's own
@@ -331,7 +331,7 @@ __global__ void __launch_bounds__(WA_DEC_WARPS * 32) attn_window_decode_vec_kern
 // tiles of 64 positions through a 2-stage cp.async pipeline, mma.sync m16n8k16 with fp32 accumulation, P = P_hi + P_lo in D.
 // Differences: the tile loop starts at the first tile the window reaches; the score gets its soft cap and distance bias
 // before the mask; ONE shared-memory tile is both the K operand of Q K^T and — read with ldmatrix.trans — the V operand of
-// P V, since the values are the keys; the head gate scales the result.  Rows are padded by 16 bytes (an odd number of
+// P V, since the keys double as values; the head gate scales the result.  Rows are padded by 16 bytes (an odd number of
 // 16-byte chunks per row keeps ldmatrix conflict-free for every head_dim, also those that are not a power of two).
 // tanh and ln use the MUFU-based __expf / __logf: |error| ~1e-6 of the score, two orders below the rounding of q and k to D.
 constexpr int WM_BM = 64, WM_BN = 64, WM_THREADS = 128;

@@ -3,7 +3,7 @@
 //   * the tile loop starting at the first tile the window of the CTA's first row reaches,
 //   * the score modifiers applied by the softmax warps before the mask (the modified score is in natural units, so the
 //     exponent constant is log2 e), rows that see nothing in a tile keeping a -inf reference,
-//   * the K tensor map given twice: the values are the keys, the V ring is filled from the same cache rows,
+//   * the K tensor map given twice: the keys double as values, the V ring is filled from the same cache rows,
 //   * the head gate and the caller's row stride in the epilogue.
 // Warp roles, barriers, TMEM layout and the P_hi + P_lo operand are those of attn_prefill_tc_kernel; see there.
 // Cost model: four MUFU operations per score (tanh = ex2 + rcp, ln, the softmax's ex2) against one in the plain kernel make

@@ -1370,7 +1370,7 @@ static int cache_ensure_listed(cake_b200_cache *k, int layer, const cake_b200_bl
   if (k->k[layer] && (k->kv_heads[layer] != nkv || k->kv_hd[layer] != hd))
     return fail(CAKE_B200_ESTATE, "block_idx %d was used with another layer geometry in this cache", layer);
   if (!k->k[layer]) {
-    CU(cudaMalloc(&k->k[layer], (size_t)k->batch * nkv * k->cap * hd * c->es + 16));  // values are the keys: no V buffer
+    CU(cudaMalloc(&k->k[layer], (size_t)k->batch * nkv * k->cap * hd * c->es + 16));  // the keys double as values: no V buffer
     k->kv_heads[layer] = nkv;
     k->kv_hd[layer] = hd;
   }

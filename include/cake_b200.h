@@ -139,10 +139,10 @@ int cake_b200_block_set_variant(cake_b200_block *, const cake_b200_block_variant
  *   token shift  the mixer reads h + (h_prev - h) * shift[hidden] where h_prev is the previous position's h (zeros at
  *                position 0); the last h of a call is kept per layer in the cache so that a prompt may be cut anywhere
  *   scores       s = (q . k) * scale;  softcap > 0: s <- softcap * tanh(s / softcap);  distance bias (r1, r2 non-NULL,
- *                one number per query head): s <- s - r1[h] * ln(1 + r2[h] * (i - j));  window > 0: position i sees
- *                j with 0 <= i - j < window (0 = every j <= i);  ordinary softmax over the visible keys, all in fp32
+ *                one number per query head): s <- s - r1[h] * ln(1 + r2[h] * (i - j));  window > 0: row i attends to
+ *                the keys j with i - window < j <= i (0 = every j <= i);  a plain softmax over the keys that row i sees, all in fp32
  *   values       values_are_keys: there is no V projection and no V cache; the output is the p-weighted sum of the keys
- *   head gate    gate non-NULL ([heads, hidden]): head h's output is multiplied by sigmoid(gate_h . shift(h))
+ *   head gate    gate non-NULL ([heads, hidden]): the output of head h is scaled by sigmoid(gate_h . shift(h))
  *   ff           ff > 0: down( act(gate_proj h) * (up h) ), act 0 = silu, 1 = tanh-gelu; ff == 0: no feed-forward
  * Weights are [out, in] row-major in D (host or device memory), q [heads*head_dim, hidden], k [kv_heads*head_dim, hidden],
  * o [hidden, heads*head_dim]. */

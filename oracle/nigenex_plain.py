@@ -39,7 +39,7 @@ def distance_bias(S, r1, r2):
 
 
 def window_mask(S, w):
-    """[S, S] bool: i sees j iff 0 <= i - j < w (w == 0: every j <= i)."""
+    """[S, S] bool: entry (i, j) is set iff i - w < j <= i (w == 0: every j <= i)."""
     i = torch.arange(S)[:, None]
     j = torch.arange(S)[None, :]
     vis = i - j >= 0
@@ -53,7 +53,7 @@ def gelu_tanh(z):
 
 
 def attention_mixer(hs, wt, sp, mm="f32"):
-    """hs [S, W] (already shifted) -> [S, W].  The values are the keys; one sigmoid gate per head from the same input."""
+    """hs [S, W] (already shifted) -> [S, W].  The keys double as values; one sigmoid gate per head, computed from hs as well."""
     S = hs.shape[0]
     H, G, D = sp.heads, sp.kv_heads, sp.head_dim
     q = linear(wt["q"], hs, mm).view(S, H, D)
