@@ -39,23 +39,53 @@ def stale() -> bool:
     return any(os.path.getmtime(s) > t for s in sources())
 
 
+# translation units of the library: object file -> (source, the files it depends on besides itself; None = everything in csrc/)
+UNITS = {
+    "cake_b200.o": ("cake_b200.cu", None),
+    "mixers.o": ("mixers.cu", ("mixers.cuh", "common.cuh")),
+}
+
+
+def _unit_stale(obj: str, src: str, deps) -> bool:
+    d = os.path.join(HERE, "csrc")
+    if not os.path.exists(obj):
+        return True
+    t = os.path.getmtime(obj)
+    files = sources() if deps is None else [os.path.join(d, src)] + [os.path.join(d, x) for x in deps]
+    return any(os.path.getmtime(f) > t for f in files)
+
+
 def build(force: bool = False, verbose: bool = False, host: bool = True, quiet: bool = False) -> str:
-    """``host=False``: only the library (what the Python host needs); ``quiet``: the compiler's output goes to stderr."""
+    """``host=False``: only the library (what the Python host needs); ``quiet``: the compiler's output goes to stderr.
+    Every translation unit is compiled to an object file beside its source (stale ones only, side by side), then linked."""
     if not force and not stale():
         if host:
             build_host()
         return SO
+    from concurrent.futures import ThreadPoolExecutor
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-    cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
-           "-ccbin", "/usr/bin/g++", "-Xcompiler", "-fPIC", "-shared", "--expt-relaxed-constexpr",
-           "-I", _nccl_include(), "-I", os.path.join(ROOT, "include"),
-           "-o", SO, SRC, "-ldl"]
+    flags = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
+             "-ccbin", "/usr/bin/g++", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
+             "-I", _nccl_include(), "-I", os.path.join(ROOT, "include")]
     if verbose:
-        cmd.insert(1, "-Xptxas")
-        cmd.insert(2, "-v")
+        flags = ["-Xptxas", "-v"] + flags
+    out = sys.stderr if quiet else None
+    d = os.path.join(HERE, "csrc")
+
+    def compile_unit(item):
+        obj, (src, deps) = item
+        obj = os.path.join(d, obj)
+        if force or _unit_stale(obj, src, deps):
+            tmp = obj + f".{os.getpid()}.tmp"
+            subprocess.check_call([nvcc, *flags, "-c", os.path.join(d, src), "-o", tmp], stdout=out)
+            os.replace(tmp, obj)
+        return obj
+
+    with ThreadPoolExecutor(max_workers=len(UNITS)) as ex:
+        objs = list(ex.map(compile_unit, UNITS.items()))
     tmp = SO + f".{os.getpid()}.tmp"   # written beside the target and renamed: a concurrent reader never maps half a library
-    cmd[cmd.index("-o") + 1] = tmp
-    subprocess.check_call(cmd, stdout=sys.stderr if quiet else None)
+    subprocess.check_call([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-ccbin", "/usr/bin/g++", "-o", tmp, *objs, "-ldl"],
+                          stdout=out)
     os.replace(tmp, SO)
     if host:
         build_host(force=True)
@@ -71,7 +101,8 @@ def build_trace(defines=("-DMK_TRACE=1",), name="libcake_b200_trace.so") -> str:
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
     subprocess.check_call([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17", *defines,
                            "-ccbin", "/usr/bin/g++", "-Xcompiler", "-fPIC", "-shared", "--expt-relaxed-constexpr",
-                           "-I", _nccl_include(), "-I", os.path.join(ROOT, "include"), "-o", out, SRC, "-ldl"])
+                           "-I", _nccl_include(), "-I", os.path.join(ROOT, "include"), "-o", out, SRC,
+                           os.path.join(HERE, "csrc", "mixers.cu"), "-ldl"])
     return out
 
 

@@ -96,6 +96,39 @@ SYMBOLS += [
 ]
 
 
+class CRotarySpec(ctypes.Structure):
+    """``cake_b200_rotary_spec`` (include/cake_b200.h)."""
+    _fields_ = [("dims", c_int), ("base", ctypes.c_double), ("yarn_factor", ctypes.c_double), ("yarn_fast", ctypes.c_double),
+                ("yarn_slow", ctypes.c_double), ("yarn_original", c_int)]
+
+
+class CMoeSpec(ctypes.Structure):
+    """``cake_b200_moe_spec`` (include/cake_b200.h)."""
+    _fields_ = [("experts", c_int), ("identity", c_int), ("top", c_int), ("scale", c_float), ("ff", c_int), ("shared_ff", c_int), ("act", c_int)]
+
+
+class CMixerSpec(ctypes.Structure):
+    """``cake_b200_mixer_spec`` (include/cake_b200.h)."""
+    _fields_ = [("kind", c_int), ("heads", c_int), ("dim", c_int), ("vdim", c_int), ("rot_dim", c_int), ("kv_rank", c_int), ("scale", c_float),
+                ("rot", CRotarySpec), ("decay", POINTER(c_float)), ("state", c_int), ("groups", c_int), ("conv", c_int), ("norm_groups", c_int),
+                ("moe", CMoeSpec)]
+
+
+MIXER_TENSOR_FIELDS = ("norm1", "norm2", "q", "k", "v", "g", "o", "dkv", "dkv_norm", "uk", "uv", "in", "conv", "conv_b", "dt_bias", "a_log", "d",
+                       "norm", "router", "correction", "e_gate", "e_up", "e_down", "s_gate", "s_up", "s_down", "s_sg")
+
+
+class CMixerTensors(ctypes.Structure):
+    """``cake_b200_mixer_tensors`` (include/cake_b200.h); e_gate / e_up / e_down are arrays of ``experts`` pointers."""
+    _fields_ = [(n, POINTER(_VP) if n.startswith("e_") else _VP) for n in MIXER_TENSOR_FIELDS]
+
+
+SYMBOLS += [
+    ("cake_b200_block_load_mixer", _I, [_VP, _I, POINTER(CMixerSpec), POINTER(CMixerTensors), POINTER(_VP)]),
+    ("cake_b200_stream_inject", _I, [_VP, _VP, _VP, _VP, _I, _I]),
+]
+
+
 class CakeB200Error(RuntimeError):
     def __init__(self, code: int, msg: str):
         super().__init__(f"cake_b200 error {code}: {msg}")

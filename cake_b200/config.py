@@ -46,6 +46,74 @@ class LayerSpec:
 
 
 @dataclass
+class RotarySpec:
+    """``cake_b200_rotary_spec``: rotation of the first ``dims`` entries of a head, pair (i, i + dims/2); ``factor`` > 0 blends
+    the frequencies towards f / factor between the pairs that complete ``fast`` and ``slow`` turns over ``original`` positions."""
+    dims: int = 0
+    base: float = 10000.0
+    factor: float = 0.0
+    fast: float = 0.0
+    slow: float = 0.0
+    original: int = 0
+
+    @staticmethod
+    def from_dict(d: Optional[dict]) -> "RotarySpec":
+        if not d:
+            return RotarySpec()
+        sc = d.get("scaling") or {}
+        return RotarySpec(dims=int(d["dims"]), base=float(d["base"]), factor=float(sc.get("factor") or 0.0), fast=float(sc.get("fast") or 0.0),
+                          slow=float(sc.get("slow") or 0.0), original=int(sc.get("original") or 0))
+
+    def to_dict(self) -> Optional[dict]:
+        if not self.dims:
+            return None
+        d = {"dims": self.dims, "base": self.base}
+        if self.factor:
+            d["scaling"] = {"factor": self.factor, "fast": self.fast, "slow": self.slow, "original": self.original}
+        return d
+
+
+@dataclass
+class MoeSpec:
+    """``cake_b200_moe_spec``: ``experts`` gated feed-forwards of width ``ff`` plus ``identity`` pass-through experts, ``top`` per
+    token, weights scaled by ``scale``; ``shared_ff`` > 0: one more expert of that width for every token, behind a sigmoid gate."""
+    experts: int = 0
+    identity: int = 0
+    top: int = 1
+    scale: float = 1.0
+    ff: int = 0
+    shared_ff: int = 0
+    act: int = 0
+
+
+MIXER_KINDS = {"latent_attention": 1, "retention": 2, "mamba2": 3}
+
+
+@dataclass
+class MixerSpec:
+    """One entry of a mixer-list config (``cake_b200_mixer_spec`` in include/cake_b200.h): a sequential pre-norm block whose
+    mixer is latent attention, retention or a state-space layer, with an optional routed feed-forward."""
+    type: str
+    heads: int
+    vdim: int
+    dim: int = 0
+    rot_dim: int = 0
+    kv_rank: int = 0
+    scale: float = 1.0
+    rot: RotarySpec = field(default_factory=RotarySpec)
+    decay: list = field(default_factory=list)
+    state: int = 0
+    groups: int = 1
+    conv: int = 1
+    norm_groups: int = 1
+    moe: Optional[MoeSpec] = None
+
+    @property
+    def inner(self) -> int:
+        return self.heads * self.vdim
+
+
+@dataclass
 class Config:
     hidden_size: int
     intermediate_size: int
@@ -76,6 +144,7 @@ class Config:
                                       # "nigenex": a layer-list model (``layers`` below), not a reference block
     layers: list = field(default_factory=list)  # layer-list models: one LayerSpec per layer (sizes differ between layers)
     logit_softcap: float = 0.0        # logits <- cap * tanh(logits / cap) after the head (0 = none)
+    loop: Optional[dict] = None       # mixer-list models: {"start", "stop", "times"}: layers start..stop-1 run `times` times in a row
 
     def layer_variant(self, i: int, max_seq: Optional[int] = None) -> dict:
         """Norm placement and attention mode of layer ``i``, as the reference's per-architecture block.rs sets them up:
@@ -107,11 +176,28 @@ class Config:
     @property
     def layer_list(self) -> bool:
         """The checkpoint's config lists its layers one by one; such models keep an fp32 residual stream."""
+        return self.block_kind in ("nigenex", "setodra")
+
+    @property
+    def scalar_final_norm(self) -> bool:
         return self.block_kind == "nigenex"
+
+    def run_plan(self) -> list:
+        """[(layer index, pass number or None)] in execution order.  Without a loop every layer runs once.  With one, the
+        layers start..stop-1 run ``times`` times with the same weights; the first layer of pass t carries t: the stream
+        receives the embedding output again (t > 0) and the pass's step vector right before it.  Every run owns a cache slot."""
+        n = len(self.layers) if self.layers else self.num_hidden_layers
+        if not self.loop:
+            return [(i, None) for i in range(n)]
+        a, b, times = int(self.loop["start"]), int(self.loop["stop"]), int(self.loop["times"])
+        runs = [(i, None) for i in range(a)]
+        for t in range(times):
+            runs += [(i, t if i == a else None) for i in range(a, b)]
+        return runs + [(i, None) for i in range(b, n)]
 
     def head_tensor_names(self):
         """(embedding, final norm, lm_head or None when tied) as the checkpoint names them (text_model.rs:159-193)."""
-        if self.block_kind == "nigenex":
+        if self.layer_list:
             return "embed", "final.norm", "head"
         p = self.model_prefix
         return f"{p}.embed_tokens.weight", f"{p}.norm.weight", None if self.tie_word_embeddings else "lm_head.weight"
@@ -131,7 +217,7 @@ class Config:
 
     def layer_name(self, i: int) -> str:
         # text_model.rs:205  "{prefix}.layers.{i}"
-        if self.block_kind == "nigenex":
+        if self.layer_list:
             return f"l{i}"
         return f"{self.model_prefix}.layers.{i}"
 
@@ -190,6 +276,64 @@ class Config:
                       rms_norm_eps=float(d["norm"]["eps"]), head_dim=specs[0].head_dim, max_seq_len=int(max_seq),
                       block_kind="nigenex", layers=specs, logit_softcap=float(d.get("logit_softcap") or 0.0), model_prefix="")
 
+    @staticmethod
+    def _from_setodra(d: dict, max_seq: int = 4096) -> "Config":
+        """Setodra ``config.json``: ``width``, ``vocab``, ``norm.eps``, ``embedding.scale``, an optional ``loop`` and ``layers``,
+        whose entries give ``type`` (latent_attention | retention | mamba2), the mixer's sizes (``mixer``) and the routed
+        feed-forward (``mlp``: kind ``moe`` with ``router``, ``expert.ff`` and an optional ``shared.ff``, or null)."""
+        specs = []
+        for i, L in enumerate(d["layers"]):
+            kind, m = L.get("type"), L["mixer"]
+            if kind not in MIXER_KINDS:
+                raise ValueError(f"layer {i}: mixer type {kind!r} is not part of this design")
+            sp = MixerSpec(type=kind, heads=int(m["heads"]), vdim=int(m["vdim"]), rot=RotarySpec.from_dict(m.get("rot")))
+            if kind == "latent_attention":
+                sp.dim, sp.rot_dim, sp.kv_rank, sp.scale = int(m["dim"]), int(m["rot_dim"]), int(m["kv_rank"]), float(m["scale"])
+            elif kind == "retention":
+                sp.dim, sp.decay = int(m["dim"]), [float(x) for x in m["decay"]]
+                if len(sp.decay) != sp.heads:
+                    raise ValueError(f"layer {i}: {len(sp.decay)} decays for {sp.heads} heads")
+            else:
+                sp.state, sp.groups, sp.conv, sp.norm_groups = int(m["state"]), int(m["groups"]), int(m["conv"]), int(m["norm_groups"])
+            mlp = L.get("mlp")
+            if mlp is not None:
+                if mlp.get("kind") != "moe":
+                    raise ValueError(f"layer {i}: feed-forward kind {mlp.get('kind')!r} is not part of this design")
+                r, sh = mlp["router"], mlp.get("shared")
+                sp.moe = MoeSpec(experts=int(r["experts"]), identity=int(r.get("identity") or 0), top=int(r["top"]), scale=float(r.get("scale", 1.0)),
+                                 ff=int((mlp.get("expert") or {}).get("ff") or 0), shared_ff=int(sh["ff"]) if sh else 0, act=0)
+            specs.append(sp)
+        if not specs:
+            raise ValueError("config lists no layers")
+        loop = d.get("loop") or None
+        if loop and not (0 <= int(loop["start"]) < int(loop["stop"]) <= len(specs) and int(loop["times"]) >= 1):
+            raise ValueError(f"bad loop {loop}")
+        cfg = Config(hidden_size=int(d["width"]), intermediate_size=0, vocab_size=int(d["vocab"]), num_hidden_layers=len(specs),
+                     num_attention_heads=specs[0].heads, num_key_value_heads=specs[0].heads, rms_norm_eps=float(d["norm"]["eps"]),
+                     head_dim=specs[0].vdim, max_seq_len=int(max_seq), block_kind="setodra", layers=specs, model_prefix="",
+                     embed_scale=float((d.get("embedding") or {}).get("scale") or 0.0) or None, loop=loop)
+        return cfg
+
+    def to_setodra(self) -> dict:
+        """The ``config.json`` of a mixer-list Config (inverse of ``_from_setodra``)."""
+        layers = []
+        for s in self.layers:
+            if s.type == "latent_attention":
+                m = {"heads": s.heads, "dim": s.dim, "rot_dim": s.rot_dim, "vdim": s.vdim, "kv_rank": s.kv_rank, "scale": s.scale, "rot": s.rot.to_dict()}
+            elif s.type == "retention":
+                m = {"heads": s.heads, "dim": s.dim, "vdim": s.vdim, "decay": list(s.decay), "rot": s.rot.to_dict()}
+            else:
+                m = {"heads": s.heads, "vdim": s.vdim, "state": s.state, "groups": s.groups, "conv": s.conv, "norm_groups": s.norm_groups}
+            mo = s.moe
+            mlp = None if mo is None else {"kind": "moe", "router": {"experts": mo.experts, "identity": mo.identity, "top": mo.top, "scale": mo.scale},
+                                           "expert": {"ff": mo.ff}, "shared": {"ff": mo.shared_ff} if mo.shared_ff else None}
+            layers.append({"type": s.type, "mixer": m, "mlp": mlp})
+        d = {"architecture": "Setodra", "width": self.hidden_size, "vocab": self.vocab_size, "norm": {"eps": self.rms_norm_eps},
+             "embedding": {"scale": self.embed_scale if self.embed_scale else 1.0}, "layers": layers}
+        if self.loop:
+            d["loop"] = dict(self.loop)
+        return d
+
     def to_nigenex(self) -> dict:
         """The ``config.json`` of a layer-list Config (inverse of ``_from_nigenex``)."""
         return {"architecture": "Nigenex", "width": self.hidden_size, "vocab": self.vocab_size, "norm": {"eps": self.rms_norm_eps},
@@ -203,6 +347,8 @@ class Config:
     def from_hf(d: dict) -> "Config":
         if d.get("architecture") == "Nigenex":  # a single string, not HF's ``architectures`` list
             return Config._from_nigenex(d)
+        if d.get("architecture") == "Setodra":
+            return Config._from_setodra(d)
         arch = Config.detect_arch(d)
         if arch in Config._OTHER_BLOCKS:
             raise ValueError(f"architecture {arch!r} is outside the block-forward path built here")
@@ -287,6 +433,8 @@ class Config:
     def to_hf(self, arch: str = "LlamaForCausalLM") -> dict:
         if self.block_kind == "nigenex":
             return self.to_nigenex()
+        if self.block_kind == "setodra":
+            return self.to_setodra()
         d = dict(
             architectures=[arch], hidden_size=self.hidden_size, intermediate_size=self.intermediate_size,
             vocab_size=self.vocab_size, num_hidden_layers=self.num_hidden_layers,
@@ -343,7 +491,7 @@ class CConfig(ctypes.Structure):
         win = int(c.sliding_window) if (c.sliding_window and c.sliding_window < (max_seq or c.max_seq_len)) else 0
         return CConfig(
             c.hidden_size, c.intermediate_size, c.num_attention_heads, c.num_key_value_heads, c.hd,
-            c.num_hidden_layers, c.vocab_size, max_seq or c.max_seq_len,
+            len(c.run_plan()) if c.layer_list else c.num_hidden_layers, c.vocab_size, max_seq or c.max_seq_len,
             c.rms_norm_eps, c.rope_theta, c.partial_rotary_factor,
             int(c.use_qkv_bias), int(c.use_qk_norm), int(c.tie_word_embeddings),
             int(llama3),
@@ -351,7 +499,7 @@ class CConfig(ctypes.Structure):
             rs.high_freq_factor if llama3 else 4.0, rs.original_max_position_embeddings if llama3 else 0,
             DTYPES[dtype],
             win, int(c.use_gelu_mlp), float(c.embed_scale or 0.0), int(c.pre_reshape_qk_norm),
-            int(c.layer_list), float(c.logit_softcap), int(c.layer_list),
+            int(c.layer_list), float(c.logit_softcap), int(c.scalar_final_norm),
         )
 
 

@@ -28,6 +28,7 @@
 #include "common.cuh"
 #include "decode_mega.cuh"
 #include "f32_stream.cuh"
+#include "mixers.cuh"
 #include "gemm_tc.cuh"
 #include "gemv.cuh"
 #include "prefill.cuh"
@@ -145,6 +146,11 @@ struct cake_b200_ctx {
   void *sp_h = nullptr, *sp_hs = nullptr, *sp_in = nullptr, *sp_a = nullptr, *sp_hn = nullptr;
   float *sp_logits = nullptr;
   int *sp_rows_idx = nullptr;
+  // mixer-list blocks: one arena for a step's scratch, grown on demand; vectors kept for cake_b200_stream_inject
+  void *mx_ws = nullptr;
+  size_t mx_ws_cap = 0;
+  void *inject_vec[64] = {};
+  const void *inject_src[64] = {};
   // comm
   ncclComm_t comm = nullptr;
   int rank = 0, world = 1;
@@ -195,6 +201,15 @@ struct cake_b200_block {
   void *w_out = nullptr;   // [hidden, heads*hd + ff] = o and down side by side along K
   void *g = nullptr, *shift = nullptr, *r1 = nullptr, *r2 = nullptr;
   int n_in = 0, n_in_pad = 0, gate_col = -1, k_out = 0;
+  // cake_b200_block_load_mixer: a sequential pre-norm block with a latent-attention / retention / state-space mixer and a
+  // routed feed-forward (w_in: the fused input projection, wo: the mixer's output projection, wgu / wd: the shared expert)
+  bool mixer = false;
+  cake_b200_mixer_spec ms{};
+  void *m_dkv_norm = nullptr, *m_uk = nullptr, *m_uv = nullptr;
+  void *m_conv = nullptr, *m_conv_b = nullptr, *m_dt_bias = nullptr, *m_a_log = nullptr, *m_d = nullptr, *m_norm = nullptr;
+  void *m_router = nullptr, *m_corr = nullptr, *m_eg = nullptr, *m_eu = nullptr, *m_ed = nullptr, *m_sg = nullptr;
+  float *m_cos = nullptr, *m_sin = nullptr, *m_decay = nullptr;
+  int m_rope_rows = 0;
   bool variant() const { return !ln1 || !ln2 || pan || pfn || window >= 0 || !use_rope || ctx->cfg.pre_reshape_qk_norm; }
 };
 
@@ -211,6 +226,9 @@ struct cake_b200_cache {
   std::vector<int> kv_heads, kv_hd;
   std::vector<float *> shift_state[2];
   std::vector<int> shift_cur;
+  // mixer-list blocks: recurrent state [batch, heads, dk, dv] fp32 and the convolution's last taps - 1 inputs, per block_idx
+  std::vector<float *> rec_state;
+  std::vector<void *> conv_hist;
 };
 
 template <typename U> struct TypeTag { typedef U type; };
@@ -529,8 +547,10 @@ extern "C" void cake_b200_ctx_destroy(cake_b200_ctx *c) {
                   c->ws_acc, c->part_val, c->part_idx, c->d_step, c->attn_counters, c->argmax_counter, c->d_token,
                   c->token_ring, c->d_ids, c->d_pen, c->pf_h, c->pf_qkv, c->pf_y, c->pf_x1, c->pf_gu, c->pf_mm, c->io_x,
                   c->gbar, c->mk_tab_dev, c->g_tab_dev, c->tickets, c->ring_seq, c->inbox, c->step_trace, c->trace,
-                  c->samp_p, c->samp_noise, c->x0, c->sp_h, c->sp_hs, c->sp_in, c->sp_a, c->sp_hn, c->sp_logits, c->sp_rows_idx};
+                  c->samp_p, c->samp_noise, c->x0, c->sp_h, c->sp_hs, c->sp_in, c->sp_a, c->sp_hn, c->sp_logits, c->sp_rows_idx, c->mx_ws};
   for (void *b : bufs)
+    if (b) cudaFree(b);
+  for (void *b : c->inject_vec)
     if (b) cudaFree(b);
   if (c->lm_head && c->lm_head != c->embed) cudaFree(c->lm_head);
   for (int i = 0; i < 2; i++) {
@@ -714,7 +734,8 @@ extern "C" void cake_b200_block_free(cake_b200_block *b) {
   if (!b) return;
   cudaSetDevice(b->device);
   void *bufs[] = {b->wqkv, b->wo, b->wgu, b->wd, b->ln1, b->ln2, b->bqkv, b->qn, b->kn, b->pan, b->pfn,
-                  b->w_in, b->w_out, b->g, b->shift, b->r1, b->r2};
+                  b->w_in, b->w_out, b->g, b->shift, b->r1, b->r2, b->m_dkv_norm, b->m_uk, b->m_uv, b->m_conv, b->m_conv_b, b->m_dt_bias,
+                  b->m_a_log, b->m_d, b->m_norm, b->m_router, b->m_corr, b->m_eg, b->m_eu, b->m_ed, b->m_sg, b->m_cos, b->m_sin, b->m_decay};
   for (void *p : bufs)
     if (p) cudaFree(p);  // cudaFree synchronises with outstanding work
   (void)cudaGetLastError();
@@ -755,6 +776,8 @@ extern "C" int cake_b200_cache_create(cake_b200_ctx *c, int batch, int max_seq, 
   k->shift_state[0].assign(c->cfg.n_layers, nullptr);
   k->shift_state[1].assign(c->cfg.n_layers, nullptr);
   k->shift_cur.assign(c->cfg.n_layers, 0);
+  k->rec_state.assign(c->cfg.n_layers, nullptr);
+  k->conv_hist.assign(c->cfg.n_layers, nullptr);
   cudaError_t e = cudaMalloc(&k->d_pos, 4);
   if (e == cudaSuccess) e = cudaMemset(k->d_pos, 0, 4);
   if (e != cudaSuccess) {
@@ -803,6 +826,10 @@ extern "C" void cake_b200_cache_free(cake_b200_cache *k) {
   for (auto &v : k->shift_state)
     for (float *p : v)
       if (p) cudaFree(p);
+  for (float *p : k->rec_state)
+    if (p) cudaFree(p);
+  for (void *p : k->conv_hist)
+    if (p) cudaFree(p);
   cudaFree(k->d_pos);
   (void)cudaGetLastError();
   delete k;
@@ -1533,6 +1560,342 @@ static int enqueue_listed_layers(cake_b200_ctx *c, cake_b200_block *const *block
   });
 }
 
+// ------------------------------------------------------------------------------------------ mixer-list blocks (fp32 residual stream)
+// include/cake_b200.h, cake_b200_mixer_spec: sequential pre-norm block; latent attention / retention / state-space mixer
+// (kernels in mixers.cu) and a routed feed-forward.  Dense projections run on the GEMMs of the layer-list blocks.
+#define MX(call)                                                                                                   \
+  do {                                                                                                             \
+    int e_ = (call);                                                                                               \
+    if (e_ != 0) return fail(CAKE_B200_ECUDA, "%s:%d %s -> %s", __FILE__, __LINE__, #call, cudaGetErrorString((cudaError_t)e_)); \
+  } while (0)
+
+// cos / sin of position * frequency for `rows` positions, in double precision, with the optional frequency blend
+static void mixer_rope_tables(const cake_b200_rotary_spec &r, int rows, std::vector<float> &cs, std::vector<float> &sn) {
+  const int half = r.dims / 2;
+  std::vector<double> f(half);
+  double amp = 1.0;
+  for (int i = 0; i < half; i++) f[i] = pow(r.base, -2.0 * i / r.dims);
+  if (r.yarn_factor > 0.0) {
+    const double pi = 3.14159265358979323846;
+    auto pair_of = [&](double turns) { return r.dims * log((double)r.yarn_original / (2.0 * pi * turns)) / (2.0 * log(r.base)); };
+    const double lo = std::max(floor(pair_of(r.yarn_fast)), 0.0), hi = std::min(ceil(pair_of(r.yarn_slow)), (double)(r.dims - 1));
+    for (int i = 0; i < half; i++) {
+      const double ramp = std::min(1.0, std::max(0.0, (i - lo) / std::max(hi - lo, 0.001)));
+      f[i] = f[i] / r.yarn_factor * ramp + f[i] * (1.0 - ramp);
+    }
+    amp = 0.1 * log(r.yarn_factor) + 1.0;
+  }
+  cs.resize((size_t)rows * half);
+  sn.resize((size_t)rows * half);
+  for (int p = 0; p < rows; p++)
+    for (int i = 0; i < half; i++) {
+      const double a = (double)p * f[i];
+      cs[(size_t)p * half + i] = (float)(cos(a) * amp);
+      sn[(size_t)p * half + i] = (float)(sin(a) * amp);
+    }
+}
+
+extern "C" int cake_b200_block_load_mixer(cake_b200_ctx *c, int layer_idx, const cake_b200_mixer_spec *sp, const cake_b200_mixer_tensors *t,
+                                          cake_b200_block **out) {
+  if (!c || !sp || !t || !out) return fail(CAKE_B200_EINVAL, "null argument");
+  if (!c->cfg.layer_list) return fail(CAKE_B200_EINVAL, "block_load_mixer needs a ctx created with layer_list = 1");
+  const cake_b200_moe_spec &mo = sp->moe;
+  const bool has_ff = mo.experts + mo.identity > 0;
+  if (sp->heads < 1 || sp->vdim < 1 || !t->norm1 || !t->o) return fail(CAKE_B200_EINVAL, "layer %d: bad heads / vdim or null norm1 / o", layer_idx);
+  if (sp->rot.dims < 0 || sp->rot.dims % 2 || (sp->rot.dims > 0 && !(sp->rot.base > 0.0))) return fail(CAKE_B200_EINVAL, "layer %d: bad rotation", layer_idx);
+  if (sp->kind == CAKE_B200_MIX_LATENT) {
+    if (sp->dim < 1 || sp->rot_dim < 0 || sp->kv_rank < 1 || sp->rot.dims > sp->rot_dim || !t->q || !t->dkv || !t->dkv_norm || !t->uk || !t->uv)
+      return fail(CAKE_B200_EINVAL, "layer %d: latent attention needs dim, kv_rank, rot.dims <= rot_dim and q / dkv / dkv_norm / uk / uv", layer_idx);
+    if (sp->kv_rank + sp->rot_dim > 768) return fail(CAKE_B200_EINVAL, "layer %d: kv_rank + rot_dim %d > 768", layer_idx, sp->kv_rank + sp->rot_dim);
+  } else if (sp->kind == CAKE_B200_MIX_RETENTION) {
+    if (sp->dim < 1 || sp->rot.dims > sp->dim || !sp->decay || !t->q || !t->k || !t->v || !t->g)
+      return fail(CAKE_B200_EINVAL, "layer %d: retention needs dim, decay, rot.dims <= dim and q / k / v / g", layer_idx);
+  } else if (sp->kind == CAKE_B200_MIX_STATE_SPACE) {
+    if (sp->state < 1 || sp->groups < 1 || sp->heads % sp->groups || sp->conv < 1 || sp->norm_groups < 1 || (sp->heads * sp->vdim) % sp->norm_groups ||
+        !t->in || !t->conv || !t->conv_b || !t->dt_bias || !t->a_log || !t->d || !t->norm)
+      return fail(CAKE_B200_EINVAL, "layer %d: state-space mixer needs state, groups | heads, conv, norm_groups | inner and its tensors", layer_idx);
+  } else return fail(CAKE_B200_EINVAL, "layer %d: mixer kind %d", layer_idx, sp->kind);
+  if (has_ff) {
+    if (mo.experts < 0 || mo.identity < 0 || mo.top < 1 || mo.top > mo.experts + mo.identity || mo.top > 32 || mo.experts + mo.identity > 256 ||
+        (mo.experts > 0 && mo.ff < 1) || mo.shared_ff < 0 || !t->norm2 || !t->router || !t->correction)
+      return fail(CAKE_B200_EINVAL, "layer %d: bad router sizes (top <= 32, experts + identity <= 256) or null norm2 / router / correction", layer_idx);
+    if (mo.experts > 0 && (!t->e_gate || !t->e_up || !t->e_down)) return fail(CAKE_B200_EINVAL, "layer %d: null expert table", layer_idx);
+    if (mo.shared_ff > 0 && (!t->s_gate || !t->s_up || !t->s_down || !t->s_sg)) return fail(CAKE_B200_EINVAL, "layer %d: null shared-expert pointer", layer_idx);
+  }
+  CU(cudaSetDevice(c->device));
+  const size_t es = c->es, H = c->cfg.hidden;
+  auto *b = new cake_b200_block{c, layer_idx, c->device};
+  b->mixer = true;
+  b->ms = *sp;
+  b->ms.decay = nullptr;
+  const int rc = [&]() -> int {
+    const size_t inner = (size_t)sp->heads * sp->vdim;
+    // the fused input projection, zero rows up to the tensor-core tile
+    std::vector<std::pair<const void *, size_t>> parts;
+    if (sp->kind == CAKE_B200_MIX_LATENT) parts = {{t->q, (size_t)sp->heads * (sp->dim + sp->rot_dim)}, {t->dkv, (size_t)sp->kv_rank + sp->rot_dim}};
+    else if (sp->kind == CAKE_B200_MIX_RETENTION) parts = {{t->q, (size_t)sp->heads * sp->dim}, {t->k, (size_t)sp->heads * sp->dim}, {t->v, inner}, {t->g, inner}};
+    else parts = {{t->in, 2 * inner + 2 * (size_t)sp->groups * sp->state + sp->heads}};
+    size_t n_in = 0;
+    for (auto &pr : parts) n_in += pr.second;
+    b->n_in = (int)n_in;
+    b->n_in_pad = round_up(b->n_in, b->n_in > 1024 ? 256 : TC_BN);
+    CU(cudaMalloc(&b->w_in, (size_t)b->n_in_pad * H * es + 16));
+    CU(cudaMemsetAsync(b->w_in, 0, (size_t)b->n_in_pad * H * es, 0));
+    CU(cudaStreamSynchronize(0));
+    size_t row = 0;
+    for (auto &pr : parts) {
+      RC(pipe_copy(c, (char *)b->w_in + row * H * es, pr.second * H * es, pr.first, pr.second * H * es, pr.second * H * es, 1));
+      row += pr.second;
+    }
+    RC(upload(c, &b->wo, t->o, H * inner * es));
+    RC(upload(c, &b->ln1, t->norm1, H * es));
+    if (sp->kind == CAKE_B200_MIX_LATENT) {
+      RC(upload(c, &b->m_dkv_norm, t->dkv_norm, (size_t)sp->kv_rank * es));
+      RC(upload(c, &b->m_uk, t->uk, (size_t)sp->heads * sp->dim * sp->kv_rank * es));
+      RC(upload(c, &b->m_uv, t->uv, inner * sp->kv_rank * es));
+    } else if (sp->kind == CAKE_B200_MIX_RETENTION) {
+      RC(upload(c, (void **)&b->m_decay, sp->decay, sp->heads * sizeof(float)));
+    } else {
+      const size_t ch = inner + 2 * (size_t)sp->groups * sp->state;
+      RC(upload(c, &b->m_conv, t->conv, ch * sp->conv * es));
+      RC(upload(c, &b->m_conv_b, t->conv_b, ch * es));
+      RC(upload(c, &b->m_dt_bias, t->dt_bias, sp->heads * es));
+      RC(upload(c, &b->m_a_log, t->a_log, sp->heads * es));
+      RC(upload(c, &b->m_d, t->d, sp->heads * es));
+      RC(upload(c, &b->m_norm, t->norm, inner * es));
+    }
+    if (sp->rot.dims > 0) {
+      std::vector<float> cs, sn;
+      b->m_rope_rows = c->cfg.max_seq;
+      mixer_rope_tables(sp->rot, b->m_rope_rows, cs, sn);
+      RC(upload(c, (void **)&b->m_cos, cs.data(), cs.size() * sizeof(float)));
+      RC(upload(c, (void **)&b->m_sin, sn.data(), sn.size() * sizeof(float)));
+      CU(cudaStreamSynchronize(c->load_stream));  // the staging copy has left the vectors
+    }
+    if (has_ff) {
+      const size_t E = mo.experts, Et = E + mo.identity, I = mo.ff, Is = mo.shared_ff;
+      RC(upload(c, &b->ln2, t->norm2, H * es));
+      RC(upload(c, &b->m_router, t->router, Et * H * es));
+      RC(upload(c, &b->m_corr, t->correction, Et * es));
+      if (E) {
+        CU(cudaMalloc(&b->m_eg, E * I * H * es + 16));
+        CU(cudaMalloc(&b->m_eu, E * I * H * es + 16));
+        CU(cudaMalloc(&b->m_ed, E * H * I * es + 16));
+        for (size_t e = 0; e < E; e++) {
+          if (!t->e_gate[e] || !t->e_up[e] || !t->e_down[e]) return fail(CAKE_B200_EINVAL, "layer %d: expert %zu has a null tensor", layer_idx, e);
+          RC(pipe_copy(c, (char *)b->m_eg + e * I * H * es, I * H * es, t->e_gate[e], I * H * es, I * H * es, 1));
+          RC(pipe_copy(c, (char *)b->m_eu + e * I * H * es, I * H * es, t->e_up[e], I * H * es, I * H * es, 1));
+          RC(pipe_copy(c, (char *)b->m_ed + e * H * I * es, H * I * es, t->e_down[e], H * I * es, H * I * es, 1));
+        }
+      }
+      if (Is) {  // the shared expert is a dense gated feed-forward: row-interleaved gate / up as everywhere else
+        CU(cudaMalloc(&b->wgu, 2 * Is * H * es + 16));
+        RC(pipe_copy(c, b->wgu, 2 * H * es, t->s_gate, H * es, H * es, Is));
+        RC(pipe_copy(c, (char *)b->wgu + H * es, 2 * H * es, t->s_up, H * es, H * es, Is));
+        RC(upload(c, &b->wd, t->s_down, H * Is * es));
+        RC(upload(c, &b->m_sg, t->s_sg, H * es));
+      }
+    }
+    return pipe_mark(c);
+  }();
+  if (rc != CAKE_B200_OK) {
+    cake_b200_block_free(b);
+    return rc;
+  }
+  *out = b;
+  return CAKE_B200_OK;
+}
+
+static int cache_ensure_mixer(cake_b200_cache *k, int layer, const cake_b200_block *b) {
+  if (layer < 0 || layer >= (int)k->k.size()) return fail(CAKE_B200_EINVAL, "block_idx %d out of range", layer);
+  cake_b200_ctx *c = k->ctx;
+  const cake_b200_mixer_spec &sp = b->ms;
+  // (kind, row width) a slot was first used with: a slot never changes its layer
+  const int tag = sp.kind, width = sp.kind == CAKE_B200_MIX_LATENT ? sp.kv_rank + sp.rot_dim
+                                  : sp.heads * (sp.kind == CAKE_B200_MIX_RETENTION ? sp.dim : sp.state) * sp.vdim;
+  if (k->kv_heads[layer] && (k->kv_heads[layer] != tag || k->kv_hd[layer] != width))
+    return fail(CAKE_B200_ESTATE, "block_idx %d was used with another layer geometry in this cache", layer);
+  if (k->kv_heads[layer]) return CAKE_B200_OK;
+  if (sp.kind == CAKE_B200_MIX_LATENT) {
+    CU(cudaMalloc(&k->k[layer], (size_t)k->batch * k->cap * width * c->es + 16));
+  } else {
+    CU(cudaMalloc(&k->rec_state[layer], (size_t)k->batch * width * sizeof(float)));
+    if (sp.kind == CAKE_B200_MIX_STATE_SPACE && sp.conv > 1)
+      CU(cudaMalloc(&k->conv_hist[layer], (size_t)k->batch * (sp.conv - 1) * (sp.heads * sp.vdim + 2 * sp.groups * sp.state) * c->es + 16));
+  }
+  k->kv_heads[layer] = tag;
+  k->kv_hd[layer] = width;
+  return CAKE_B200_OK;
+}
+
+// scratch of one block for M rows, carved from the ctx arena (base == nullptr: sizes only)
+struct MixerScratch {
+  void *h, *proj, *qa, *lat, *att, *conv, *act, *sact;
+  float *o32, *wts, *sgate, *y;
+  int *ids, *counts, *perm, *tile_expert, *tile_row0, *tile_rows, *n_tiles;
+  int max_tiles;
+  size_t total;
+};
+static MixerScratch mixer_scratch(const cake_b200_ctx *c, const cake_b200_block *b, size_t M, char *base) {
+  MixerScratch s{};
+  size_t off = 0;
+  auto take = [&](size_t bytes) -> void * {
+    void *p = base ? base + off : nullptr;
+    off += (bytes + 255) / 256 * 256;
+    return p;
+  };
+  const cake_b200_mixer_spec &sp = b->ms;
+  const size_t es = c->es, H = c->cfg.hidden, inner = (size_t)sp.heads * sp.vdim;
+  s.h = take(M * H * es);
+  s.proj = take(M * b->n_in_pad * es);
+  s.att = take(M * inner * es);
+  if (sp.kind == CAKE_B200_MIX_LATENT) {
+    s.qa = take(M * sp.heads * (sp.kv_rank + sp.rot_dim) * es);
+    s.lat = take(M * sp.heads * sp.kv_rank * es);
+  } else {
+    s.o32 = (float *)take(M * inner * sizeof(float));
+    if (sp.kind == CAKE_B200_MIX_STATE_SPACE) s.conv = take(M * (inner + 2 * (size_t)sp.groups * sp.state) * es);
+  }
+  const cake_b200_moe_spec &mo = sp.moe;
+  if (mo.experts + mo.identity > 0) {
+    const size_t nt = M * mo.top;
+    s.max_tiles = (int)((nt + 63) / 64 + mo.experts);
+    s.ids = (int *)take(nt * sizeof(int));
+    s.wts = (float *)take(nt * sizeof(float));
+    s.sgate = (float *)take(M * sizeof(float));
+    s.counts = (int *)take((mo.experts + 1) * sizeof(int));
+    s.perm = (int *)take(nt * sizeof(int));
+    s.tile_expert = (int *)take(s.max_tiles * sizeof(int));
+    s.tile_row0 = (int *)take(s.max_tiles * sizeof(int));
+    s.tile_rows = (int *)take(s.max_tiles * sizeof(int));
+    s.n_tiles = (int *)take(sizeof(int));
+    if (mo.experts) {
+      s.act = take(nt * mo.ff * es);
+      s.y = (float *)take(nt * H * sizeof(float));
+    }
+    if (mo.shared_ff) s.sact = take(M * mo.shared_ff * es);
+  }
+  s.total = off;
+  return s;
+}
+
+// x_in, x_out: [B, S, hidden] fp32 (may alias)
+static int enqueue_mixer_layers(cake_b200_ctx *c, cake_b200_block *const *blocks, const int *block_idx, int n, cake_b200_cache *kc,
+                                const float *x_in, float *x_out, int B, int S, int pos0) {
+  const int H = c->cfg.hidden, M = B * S, dt = c->cfg.dtype;
+  size_t need = 0;
+  for (int i = 0; i < n; i++) {
+    need = std::max(need, mixer_scratch(c, blocks[i], (size_t)M, nullptr).total);
+    if (blocks[i]->m_cos && pos0 + S > blocks[i]->m_rope_rows)
+      return fail(CAKE_B200_ESTATE, "position %d exceeds the rotation table (%d rows = the ctx's max_seq)", pos0 + S, blocks[i]->m_rope_rows);
+  }
+  if (need > c->mx_ws_cap) {
+    CU(cudaStreamSynchronize(c->stream));
+    if (c->mx_ws) cudaFree(c->mx_ws);
+    c->mx_ws = nullptr;
+    c->mx_ws_cap = 0;
+    CU(cudaMalloc(&c->mx_ws, need));
+    c->mx_ws_cap = need;
+  }
+  cudaStream_t st = c->stream;
+  uint64_t *lc = c->capturing ? &c->g_kernels : &c->launches;
+  return DISPATCH_T3(dt, T_LAMBDA {
+    typedef typename decltype(tag_)::type T;
+    const float *cur = x_in;
+    for (int i = 0; i < n; i++) {
+      const cake_b200_block *b = blocks[i];
+      const cake_b200_mixer_spec &sp = b->ms;
+      const int l = block_idx[i], inner = sp.heads * sp.vdim;
+      const MixerScratch w = mixer_scratch(c, b, (size_t)M, (char *)c->mx_ws);
+      // 1. h = norm1(x); every input projection of the mixer in one product
+      RC(launch_pdl(c, norm_shift_rows_kernel<T>, dim3(M), dim3(256), 0, cur, (const int *)nullptr, 1, 0, (const T *)b->ln1, 1, (const T *)nullptr,
+                    (const float *)nullptr, (float *)nullptr, (T *)w.h, (T *)nullptr, S, H, c->cfg.rms_eps, pos0));
+      RowsGemm gi{w.h, b->w_in, nullptr, w.proj, M, b->n_in, H, H, b->n_in_pad, 0, 0.f};
+      if (listed_tc<T>(c, M, b->n_in_pad, H)) RC((listed_gemm_tc<T, TCE_PLAIN>(c, w.h, b->w_in, nullptr, w.proj, M, b->n_in_pad, H, 0, 0)));
+      else RC((gemm_rows_T<T, RE_STORE>(c, gi)));
+      // 2. the mixer: [M, inner] in D
+      if (sp.kind == CAKE_B200_MIX_LATENT) {
+        const int Dk = sp.kv_rank + sp.rot_dim, qw = sp.dim + sp.rot_dim;
+        mx::LatentPrep lp{w.proj, b->n_in_pad, sp.heads * qw, b->m_dkv_norm, b->m_cos, b->m_sin, sp.rot.dims, kc->k[l], w.qa,
+                          B, S, sp.heads, sp.dim, sp.rot_dim, sp.kv_rank, kc->cap, pos0, c->cfg.rms_eps};
+        MX(mx::latent_prep(st, dt, lp, lc));
+        // the unrotated query through the key expansion: qa[m, h, :rank] = q[m, h, :dim] . uk[h]   (uk[h]: [dim, rank])
+        mx::HeadGemm ga{w.proj, b->m_uk, w.qa, M, sp.kv_rank, sp.dim, sp.heads, qw, (long)sp.dim * sp.kv_rank, Dk, b->n_in_pad, sp.kv_rank, sp.heads * Dk, 1};
+        MX(mx::head_gemm(st, dt, ga, lc));
+        mx::LatentAttn la{w.qa, kc->k[l], w.lat, B, S, sp.heads, sp.kv_rank, sp.rot_dim, kc->cap, pos0, sp.scale};
+        MX(mx::latent_attention(st, dt, la, lc));
+        // the weighted latent through the value expansion: att[m, h, :] = uv[h] lat[m, h]   (uv[h]: [vdim, rank])
+        mx::HeadGemm gv{w.lat, b->m_uv, w.att, M, sp.vdim, sp.kv_rank, sp.heads, sp.kv_rank, (long)sp.vdim * sp.kv_rank, sp.vdim,
+                        sp.heads * sp.kv_rank, sp.kv_rank, inner, 0};
+        MX(mx::head_gemm(st, dt, gv, lc));
+      } else if (sp.kind == CAKE_B200_MIX_RETENTION) {
+        const int qk = sp.heads * sp.dim;
+        const T *pj = (const T *)w.proj;
+        mx::Recurrence r{pj, pj + qk, pj + 2 * qk, b->n_in_pad, b->n_in_pad, b->n_in_pad, 1, nullptr, 0, nullptr, nullptr, nullptr, b->m_decay,
+                         1.0f / sqrtf((float)sp.dim), b->m_cos, b->m_sin, sp.rot.dims, kc->rec_state[l], w.o32, B, S, sp.heads, sp.dim, sp.vdim, pos0};
+        MX(mx::recurrence(st, dt, r, lc));
+        mx::GateNorm gn{w.o32, pj + 2 * qk + inner, b->n_in_pad, nullptr, w.att, M, inner, sp.heads, 0, c->cfg.rms_eps};
+        MX(mx::gate_norm(st, dt, gn, lc));
+      } else {
+        const int gn_ = sp.groups * sp.state, ch = inner + 2 * gn_;
+        const T *pj = (const T *)w.proj, *cv = (const T *)w.conv;
+        mx::ShortConv sc{pj, b->n_in_pad, inner, b->m_conv, b->m_conv_b, kc->conv_hist[l], w.conv, B, S, ch, sp.conv, pos0};
+        MX(mx::short_conv(st, dt, sc, lc));
+        mx::Recurrence r{cv + inner + gn_, cv + inner, cv, ch, ch, ch, sp.heads / sp.groups, pj + inner + ch, b->n_in_pad, b->m_dt_bias, b->m_a_log, b->m_d,
+                         nullptr, 1.0f, nullptr, nullptr, 0, kc->rec_state[l], w.o32, B, S, sp.heads, sp.state, sp.vdim, pos0};
+        MX(mx::recurrence(st, dt, r, lc));
+        mx::GateNorm gn{w.o32, pj, b->n_in_pad, b->m_norm, w.att, M, inner, sp.norm_groups, 1, c->cfg.rms_eps};
+        MX(mx::gate_norm(st, dt, gn, lc));
+      }
+      // 3. x <- x + o(att)
+      RowsGemm go{w.att, b->wo, cur, x_out, M, H, inner, inner, H, 0, 0.f};
+      if (listed_tc<T>(c, M, H, inner) && (((uintptr_t)cur | (uintptr_t)x_out) & 15) == 0)
+        RC((listed_gemm_tc<T, TCE_RESIDUAL_F32>(c, w.att, b->wo, cur, x_out, M, H, inner, 0, 0)));
+      else RC((gemm_rows_T<T, RE_RESIDUAL_F32>(c, go)));
+      cur = x_out;
+      // 4. x <- x + routed experts(norm2(x)) + gate * shared expert
+      const cake_b200_moe_spec &mo = sp.moe;
+      if (mo.experts + mo.identity > 0) {
+        RC(launch_pdl(c, norm_shift_rows_kernel<T>, dim3(M), dim3(256), 0, cur, (const int *)nullptr, 1, 0, (const T *)b->ln2, 1, (const T *)nullptr,
+                      (const float *)nullptr, (float *)nullptr, (T *)w.h, (T *)nullptr, S, H, c->cfg.rms_eps, pos0));
+        mx::MoePlan mp{w.h, b->m_router, b->m_corr, mo.shared_ff ? b->m_sg : nullptr, M, H, mo.experts, mo.identity, mo.top, mo.scale, w.ids, w.wts,
+                       w.sgate, 64, w.counts, w.perm, w.tile_expert, w.tile_row0, w.tile_rows, w.n_tiles, w.max_tiles};
+        MX(mx::moe_route(st, dt, mp, lc));
+        if (mo.experts) {
+          mx::MoeExperts me{w.h, b->m_eg, b->m_eu, b->m_ed, w.act, w.y, M, H, mo.ff, mo.top, mo.act, w.perm, w.tile_expert, w.tile_row0, w.tile_rows,
+                            w.n_tiles, w.wts, 64, w.max_tiles};
+          MX(mx::moe_experts(st, dt, me, lc));
+        }
+        mx::MoeCombine mc{cur, x_out, w.h, w.y, w.wts, w.ids, M, H, mo.top, mo.experts};
+        MX(mx::moe_combine(st, dt, mc, lc));
+        if (mo.shared_ff) {
+          RowsGemm gu{w.h, b->wgu, nullptr, w.sact, M, 2 * mo.shared_ff, H, H, mo.shared_ff, mo.act, 0.f};
+          if (listed_tc<T>(c, M, 2 * mo.shared_ff, H)) RC((listed_gemm_tc<T, TCE_SWIGLU>(c, w.h, b->wgu, nullptr, w.sact, M, 2 * mo.shared_ff, H, mo.act, mo.shared_ff)));
+          else RC((gemm_rows_T<T, RE_GATE_UP>(c, gu)));
+          RowsGemm gd{w.sact, b->wd, x_out, x_out, M, H, mo.shared_ff, mo.shared_ff, H, 0, 0.f, w.sgate};
+          RC((gemm_rows_T<T, RE_RESIDUAL_F32>(c, gd)));
+        }
+      }
+    }
+    return CAKE_B200_OK;
+  });
+}
+
+extern "C" int cake_b200_stream_inject(cake_b200_ctx *c, float *x_dev, const float *x0_dev, const void *vec, int slot, int rows) {
+  if (!c || !x_dev || !vec || rows < 1 || slot < 0 || slot >= 64) return fail(CAKE_B200_EINVAL, "bad stream_inject arguments");
+  if (!c->cfg.layer_list) return fail(CAKE_B200_EINVAL, "stream_inject is for models with an fp32 residual stream");
+  CU(cudaSetDevice(c->device));
+  if (c->inject_src[slot] != vec) {
+    if (c->inject_vec[slot]) { CU(cudaStreamSynchronize(c->stream)); cudaFree(c->inject_vec[slot]); c->inject_vec[slot] = nullptr; }
+    RC(upload(c, &c->inject_vec[slot], vec, (size_t)c->cfg.hidden * c->es));
+    RC(pipe_mark(c));
+    c->inject_src[slot] = vec;
+  }
+  RC(wait_loads(c));
+  MX(mx::stream_inject(c->stream, c->cfg.dtype, x_dev, x0_dev, c->inject_vec[slot], rows, c->cfg.hidden, &c->launches));
+  return CAKE_B200_OK;
+}
+
 // ------------------------------------------------------------------------------------------ forward_batch
 extern "C" int cake_b200_forward_batch(cake_b200_ctx *c, cake_b200_block *const *blocks, const int *block_idx,
                                        int n_blocks, cake_b200_cache *kc, const void *x_dev, void *y_dev, int batch,
@@ -1543,18 +1906,26 @@ extern "C" int cake_b200_forward_batch(cake_b200_ctx *c, cake_b200_block *const 
     return fail(CAKE_B200_ESTATE, "index_pos %d + seq %d exceeds cache capacity %d", index_pos, seq, kc->cap);
   CU(cudaSetDevice(c->device));
   RC(wait_loads(c));
-  bool listed = false;
+  bool listed = false, mixer = false;
   for (int i = 0; i < n_blocks; i++) {
     if (!blocks[i]) return fail(CAKE_B200_EINVAL, "blocks[%d] is null", i);
     listed = listed || blocks[i]->listed;
-    if (blocks[i]->listed != listed) return fail(CAKE_B200_EINVAL, "layer-list blocks and Llama-family blocks cannot share a call");
+    mixer = mixer || blocks[i]->mixer;
+    if (blocks[i]->listed != listed || blocks[i]->mixer != mixer) return fail(CAKE_B200_EINVAL, "blocks of different families cannot share a call");
   }
   for (int i = 0; i < n_blocks; i++) {
-    if (listed) RC(cache_ensure_listed(kc, block_idx[i], blocks[i]));
+    if (mixer) RC(cache_ensure_mixer(kc, block_idx[i], blocks[i]));
+    else if (listed) RC(cache_ensure_listed(kc, block_idx[i], blocks[i]));
     else RC(cache_ensure(kc, block_idx[i]));
     if (kc->len[block_idx[i]] != index_pos)
       return fail(CAKE_B200_ESTATE, "block %d: index_pos %d != cache length %d (clear the cache or feed positions in order)",
                   block_idx[i], index_pos, kc->len[block_idx[i]]);
+  }
+  if (mixer) {  // fp32 residual stream
+    RC(enqueue_mixer_layers(c, blocks, block_idx, n_blocks, kc, (const float *)x_dev, (float *)y_dev, batch, seq, index_pos));
+    for (int i = 0; i < n_blocks; i++) kc->len[block_idx[i]] = index_pos + seq;
+    CU(cudaGetLastError());
+    return CAKE_B200_OK;
   }
   if (listed) {  // fp32 residual stream: x_dev / y_dev are float
     RC(enqueue_listed_layers(c, blocks, block_idx, n_blocks, kc, (const float *)x_dev, (float *)y_dev, batch, seq, index_pos));

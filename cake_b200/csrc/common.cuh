@@ -25,6 +25,11 @@ template <> struct DT<__half> {
     return __half22float2(*reinterpret_cast<const __half2 *>(&u));
   }
 };
+// D = float: layer-list and mixer-list models in true fp32
+template <> struct DT<float> {
+  static __device__ __forceinline__ float to_f(float v) { return v; }
+  static __device__ __forceinline__ float from_f(float f) { return f; }
+};
 // round-trip through D: the "->D" rounding points of the reference
 template <typename T> __device__ __forceinline__ float rnd(float f) { return DT<T>::to_f(DT<T>::from_f(f)); }
 

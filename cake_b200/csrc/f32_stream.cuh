@@ -16,11 +16,6 @@
 
 namespace cake {
 
-template <> struct DT<float> {
-  static __device__ __forceinline__ float to_f(float v) { return v; }
-  static __device__ __forceinline__ float from_f(float f) { return f; }
-};
-
 // ---- embedding gather into the fp32 stream ------------------------------------------------------------------------------
 template <typename T> struct EmbedBits { typedef T type; };
 template <> struct EmbedBits<float> { typedef __nv_bfloat16 type; };  // never taken for float (sizeof test); keeps unpack8 instantiable
@@ -165,6 +160,7 @@ struct RowsGemm {
   int M, N, K, lda, ldc;
   int act;          // RE_GATE_UP: 0 silu, 1 tanh-gelu
   float cap;        // RE_SOFTCAP_F32: 0 = none
+  const float *rs = nullptr;  // RE_RESIDUAL_F32: optional [M] fp32, C = R + rs[m] * (A W^T) (a per-row gate on the product)
 };
 constexpr int RG_BM = 64, RG_BN = 64, RG_BK = 16;
 template <typename T, int EPI>
@@ -214,7 +210,7 @@ __global__ void __launch_bounds__(256) gemm_rows_kernel(const RowsGemm p) {
         const int n = n0 + tx * 4 + j;
         if (n >= p.N) continue;
         if (EPI == RE_STORE) reinterpret_cast<T *>(p.C)[(size_t)m * p.ldc + n] = DT<T>::from_f(acc[i][j]);
-        else if (EPI == RE_RESIDUAL_F32) reinterpret_cast<float *>(p.C)[(size_t)m * p.N + n] = p.R[(size_t)m * p.N + n] + acc[i][j];
+        else if (EPI == RE_RESIDUAL_F32) reinterpret_cast<float *>(p.C)[(size_t)m * p.N + n] = p.R[(size_t)m * p.N + n] + (p.rs ? p.rs[m] * acc[i][j] : acc[i][j]);
         else reinterpret_cast<float *>(p.C)[(size_t)m * p.N + n] = p.cap > 0.f ? p.cap * tanhf(acc[i][j] / p.cap) : acc[i][j];
       }
     }

@@ -1,0 +1,589 @@
+// mixers.cu — kernels behind mixers.cuh: latent attention, gated linear recurrences, short convolutions, gated unit norms
+// and the routed feed-forward of mixer-list blocks.  sm_100a only.  fp32 everywhere the interface says so; D only where a
+// projection, a cache row or a weight is stored.
+#include "mixers.cuh"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <math.h>
+
+#include "common.cuh"
+
+namespace cake {
+namespace mx {
+
+#define MX_DISPATCH(dtype, ...)                               \
+  do {                                                        \
+    if ((dtype) == 2) { typedef float T; __VA_ARGS__; }       \
+    else if ((dtype) == 1) { typedef __half T; __VA_ARGS__; } \
+    else { typedef __nv_bfloat16 T; __VA_ARGS__; }            \
+  } while (0)
+#define MX_DONE(n)                     \
+  do {                                 \
+    if (launches) *launches += (n);    \
+    return (int)cudaGetLastError();    \
+  } while (0)
+
+__device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
+__device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
+
+// rotate entry i of a vector whose first `dims` entries are paired (i, i + dims/2); cs / sn: this position's table row
+template <typename T>
+__device__ __forceinline__ float rotated(const T *v, int i, int dims, const float *cs, const float *sn) {
+  const int half = dims >> 1;
+  if (i >= dims) return DT<T>::to_f(v[i]);
+  if (i < half) return DT<T>::to_f(v[i]) * cs[i] - DT<T>::to_f(v[i + half]) * sn[i];
+  return DT<T>::to_f(v[i]) * cs[i - half] + DT<T>::to_f(v[i - half]) * sn[i - half];
+}
+
+// ---------------------------------------------------------------------------------------------- latent attention: prep
+template <typename T>
+__global__ void __launch_bounds__(128) latent_prep_kernel(const LatentPrep p) {
+  __shared__ float red[4];
+  const int m = blockIdx.x, b = m / p.S, t = m % p.S, pos = p.pos0 + t;
+  const T *row = reinterpret_cast<const T *>(p.proj) + (size_t)m * p.ld;
+  const T *kv = row + p.kv_col;
+  const int Dk = p.rank + p.rot, half = p.rope_dims >> 1;
+  const float *cs = p.cos_t + (size_t)pos * half, *sn = p.sin_t + (size_t)pos * half;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < p.rank; i += blockDim.x) {
+    const float v = DT<T>::to_f(kv[i]);
+    ss = fmaf(v, v, ss);
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  const float inv = 1.0f / sqrtf((red[0] + red[1] + red[2] + red[3]) / (float)p.rank + p.eps);
+  T *crow = reinterpret_cast<T *>(p.cache) + ((size_t)b * p.cap + pos) * Dk;
+  const T *w = reinterpret_cast<const T *>(p.norm_w);
+  for (int i = threadIdx.x; i < p.rank; i += blockDim.x) crow[i] = DT<T>::from_f(DT<T>::to_f(kv[i]) * inv * DT<T>::to_f(w[i]));
+  for (int i = threadIdx.x; i < p.rot; i += blockDim.x) crow[p.rank + i] = DT<T>::from_f(rotated<T>(kv + p.rank, i, p.rope_dims, cs, sn));
+  T *qa = reinterpret_cast<T *>(p.qa) + (size_t)m * p.heads * Dk;
+  for (int i = threadIdx.x; i < p.heads * p.rot; i += blockDim.x) {
+    const int h = i / p.rot, r = i % p.rot;
+    qa[(size_t)h * Dk + p.rank + r] = DT<T>::from_f(rotated<T>(row + (size_t)h * (p.dim + p.rot) + p.dim, r, p.rope_dims, cs, sn));
+  }
+}
+int latent_prep(cudaStream_t st, int dtype, const LatentPrep &p, uint64_t *launches) {
+  MX_DISPATCH(dtype, (latent_prep_kernel<T><<<p.B * p.S, 128, 0, st>>>(p)));
+  MX_DONE(1);
+}
+
+// ---------------------------------------------------------------------------------------------- latent attention: core
+// One warp per (row, head): lanes split the rank + rot columns of a cached row, four keys per round, running softmax.
+template <typename T, int NR>
+__global__ void __launch_bounds__(128) latent_attn_kernel(const LatentAttn p) {
+  const int warp = (int)(((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5), lane = threadIdx.x & 31;
+  if (warp >= p.B * p.S * p.heads) return;
+  const int m = warp / p.heads, h = warp % p.heads, b = m / p.S, t = m % p.S, n_keys = p.pos0 + t + 1;
+  const int Dk = p.rank + p.rot;
+  const T *q = reinterpret_cast<const T *>(p.qa) + ((size_t)m * p.heads + h) * Dk;
+  const T *kc = reinterpret_cast<const T *>(p.cache) + (size_t)b * p.cap * Dk;
+  float qv[NR], acc[NR];
+#pragma unroll
+  for (int i = 0; i < NR; i++) {
+    const int c = lane + 32 * i;
+    qv[i] = c < Dk ? DT<T>::to_f(q[c]) * p.scale : 0.f;
+    acc[i] = 0.f;
+  }
+  float mx = -INFINITY, l = 0.f;
+  for (int j = 0; j < n_keys; j += 4) {
+    float kv[4][NR], s[4];
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      const bool ok = j + u < n_keys;
+      const T *row = kc + (size_t)(ok ? j + u : j) * Dk;
+      float part = 0.f;
+#pragma unroll
+      for (int i = 0; i < NR; i++) {
+        const int c = lane + 32 * i;
+        kv[u][i] = c < Dk ? DT<T>::to_f(row[c]) : 0.f;
+        part = fmaf(qv[i], kv[u][i], part);
+      }
+      s[u] = part;
+    }
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      s[u] = warp_sum(s[u]);
+      if (j + u >= n_keys) s[u] = -INFINITY;
+    }
+    const float mn = fmaxf(fmaxf(mx, fmaxf(s[0], s[1])), fmaxf(s[2], s[3]));
+    const float corr = expf(mx - mn);  // first round: exp(-inf) = 0
+    float pr[4];
+#pragma unroll
+    for (int u = 0; u < 4; u++) pr[u] = expf(s[u] - mn);
+    l = l * corr + ((pr[0] + pr[1]) + (pr[2] + pr[3]));
+#pragma unroll
+    for (int i = 0; i < NR; i++) {
+      float a = acc[i] * corr;
+#pragma unroll
+      for (int u = 0; u < 4; u++) a = fmaf(pr[u], kv[u][i], a);
+      acc[i] = a;
+    }
+    mx = mn;
+  }
+  T *out = reinterpret_cast<T *>(p.lat) + ((size_t)m * p.heads + h) * p.rank;
+  const float il = 1.0f / l;
+#pragma unroll
+  for (int i = 0; i < NR; i++) {
+    const int c = lane + 32 * i;
+    if (c < p.rank) out[c] = DT<T>::from_f(acc[i] * il);
+  }
+}
+int latent_attention(cudaStream_t st, int dtype, const LatentAttn &p, uint64_t *launches) {
+  const int Dk = p.rank + p.rot;
+  if (Dk > 32 * 24) return (int)cudaErrorInvalidValue;
+  const long warps = (long)p.B * p.S * p.heads;
+  const unsigned grid = (unsigned)((warps + 3) / 4);
+  MX_DISPATCH(dtype, {
+    if (Dk <= 32 * 6) latent_attn_kernel<T, 6><<<grid, 128, 0, st>>>(p);
+    else if (Dk <= 32 * 12) latent_attn_kernel<T, 12><<<grid, 128, 0, st>>>(p);
+    else latent_attn_kernel<T, 24><<<grid, 128, 0, st>>>(p);
+  });
+  MX_DONE(1);
+}
+
+// ---------------------------------------------------------------------------------------------- batched small products
+constexpr int HG_BM = 64, HG_BN = 64, HG_BK = 16;
+template <typename T>
+__global__ void __launch_bounds__(256) head_gemm_kernel(const HeadGemm p) {
+  __shared__ float As[HG_BK][HG_BM + 4];
+  __shared__ float Ws[HG_BK][HG_BN + 4];
+  const int z = blockIdx.z;
+  const T *A = reinterpret_cast<const T *>(p.A) + (size_t)z * p.a_zs;
+  const T *W = reinterpret_cast<const T *>(p.W) + (size_t)z * p.w_zs;
+  T *C = reinterpret_cast<T *>(p.C) + (size_t)z * p.c_zs;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int m0 = blockIdx.y * HG_BM, n0 = blockIdx.x * HG_BN;
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < p.K; k0 += HG_BK) {
+    for (int i = threadIdx.x; i < HG_BM * HG_BK; i += 256) {
+      const int r = i / HG_BK, c = i % HG_BK;
+      As[c][r] = (m0 + r < p.M && k0 + c < p.K) ? DT<T>::to_f(A[(size_t)(m0 + r) * p.lda + k0 + c]) : 0.f;
+    }
+    if (p.w_kn) {
+      for (int i = threadIdx.x; i < HG_BN * HG_BK; i += 256) {
+        const int c = i / HG_BN, r = i % HG_BN;  // consecutive threads walk n: W[k][n] is contiguous along n
+        Ws[c][r] = (n0 + r < p.N && k0 + c < p.K) ? DT<T>::to_f(W[(size_t)(k0 + c) * p.ldw + n0 + r]) : 0.f;
+      }
+    } else {
+      for (int i = threadIdx.x; i < HG_BN * HG_BK; i += 256) {
+        const int r = i / HG_BK, c = i % HG_BK;
+        Ws[c][r] = (n0 + r < p.N && k0 + c < p.K) ? DT<T>::to_f(W[(size_t)(n0 + r) * p.ldw + k0 + c]) : 0.f;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < HG_BK; k++) {
+      float av[4], wv[4];
+#pragma unroll
+      for (int i = 0; i < 4; i++) { av[i] = As[k][ty * 4 + i]; wv[i] = Ws[k][tx * 4 + i]; }
+#pragma unroll
+      for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const int m = m0 + ty * 4 + i;
+    if (m >= p.M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const int n = n0 + tx * 4 + j;
+      if (n < p.N) C[(size_t)m * p.ldc + n] = DT<T>::from_f(acc[i][j]);
+    }
+  }
+}
+int head_gemm(cudaStream_t st, int dtype, const HeadGemm &p, uint64_t *launches) {
+  dim3 grid((p.N + HG_BN - 1) / HG_BN, (p.M + HG_BM - 1) / HG_BM, p.Z);
+  MX_DISPATCH(dtype, (head_gemm_kernel<T><<<grid, 256, 0, st>>>(p)));
+  MX_DONE(1);
+}
+
+// ---------------------------------------------------------------------------------------------- gated linear recurrence
+// One CTA per (head, batch row) walks the step's tokens in order.  The state sits in shared memory; thread (j, s) owns
+// column j of the rows i = s, s + RS, ...: it updates them and adds S[i][j] q[i] to its partial of o[j].
+template <typename T>
+__global__ void recurrence_kernel(const Recurrence p) {
+  extern __shared__ float sm[];
+  const int h = blockIdx.x, b = blockIdx.y, dk = p.dk, dv = p.dv;
+  const int RS = max(1, (int)blockDim.x / dv);
+  float *St = sm, *qs = St + (size_t)dk * dv, *ks = qs + dk, *vs = ks + dk, *part = vs + dv;
+  float *gstate = p.state + ((size_t)b * p.heads + h) * dk * dv;
+  for (int i = threadIdx.x; i < dk * dv; i += blockDim.x) St[i] = p.pos0 > 0 ? gstate[i] : 0.f;
+  const int gcol = (h / p.group_div) * dk, half = p.rope_dims >> 1;
+  const T *dtb = reinterpret_cast<const T *>(p.dt_bias), *alog = reinterpret_cast<const T *>(p.a_log), *skp = reinterpret_cast<const T *>(p.skip);
+  const float nexpA = p.dt ? -expf(DT<T>::to_f(alog[h])) : 0.f, bias = p.dt ? DT<T>::to_f(dtb[h]) : 0.f;
+  const float skip = skp ? DT<T>::to_f(skp[h]) : 0.f;
+  const int j = threadIdx.x % dv, s = threadIdx.x / dv;
+  const bool owner = s < RS;
+  for (int t = 0; t < p.S; t++) {
+    const size_t m = (size_t)b * p.S + t;
+    const T *qr = reinterpret_cast<const T *>(p.q) + m * p.ldq + gcol;
+    const T *kr = reinterpret_cast<const T *>(p.k) + m * p.ldk + gcol;
+    const T *vr = reinterpret_cast<const T *>(p.v) + m * p.ldv + (size_t)h * dv;
+    float a, bsc;
+    if (p.dt) {
+      const float d = softplus_f(DT<T>::to_f(reinterpret_cast<const T *>(p.dt)[m * p.lddt + h]) + bias);
+      a = expf(nexpA * d);
+      bsc = d;
+    } else {
+      a = p.decay[h];
+      bsc = p.kscale;
+    }
+    const float *cs = p.cos_t ? p.cos_t + (size_t)(p.pos0 + t) * half : nullptr, *sn = p.sin_t ? p.sin_t + (size_t)(p.pos0 + t) * half : nullptr;
+    for (int i = threadIdx.x; i < dk; i += blockDim.x) {
+      if (cs) {
+        qs[i] = rotated<T>(qr, i, p.rope_dims, cs, sn);
+        ks[i] = rotated<T>(kr, i, p.rope_dims, cs, sn) * bsc;
+      } else {
+        qs[i] = DT<T>::to_f(qr[i]);
+        ks[i] = DT<T>::to_f(kr[i]) * bsc;
+      }
+    }
+    for (int i = threadIdx.x; i < dv; i += blockDim.x) vs[i] = DT<T>::to_f(vr[i]);
+    __syncthreads();
+    if (owner) {
+      for (int jj = j; jj < dv; jj += blockDim.x) {  // one pass unless dv exceeds the block
+        const float v = vs[jj];
+        float acc = 0.f;
+        for (int i = s; i < dk; i += RS) {
+          const float sn_ = fmaf(a, St[(size_t)i * dv + jj], ks[i] * v);
+          St[(size_t)i * dv + jj] = sn_;
+          acc = fmaf(sn_, qs[i], acc);
+        }
+        part[(size_t)s * dv + jj] = acc;
+      }
+    }
+    __syncthreads();
+    for (int jj = threadIdx.x; jj < dv; jj += blockDim.x) {
+      float o = 0.f;
+      for (int r = 0; r < RS; r++) o += part[(size_t)r * dv + jj];
+      p.o[m * ((size_t)p.heads * dv) + (size_t)h * dv + jj] = fmaf(skip, vs[jj], o);
+    }
+    __syncthreads();
+  }
+  for (int i = threadIdx.x; i < dk * dv; i += blockDim.x) gstate[i] = St[i];
+}
+int recurrence(cudaStream_t st, int dtype, const Recurrence &p, uint64_t *launches) {
+  if (p.dv > 1024 || p.dk < 1) return (int)cudaErrorInvalidValue;
+  const int threads = p.dv <= 256 ? 256 : (p.dv + 31) / 32 * 32;
+  const int RS = threads / p.dv > 0 ? threads / p.dv : 1;
+  const size_t smem = ((size_t)p.dk * p.dv + 2 * p.dk + p.dv + (size_t)RS * p.dv) * sizeof(float);
+  if (smem > 227 * 1024) return (int)cudaErrorInvalidValue;
+  MX_DISPATCH(dtype, {
+    cudaError_t e = cudaFuncSetAttribute(recurrence_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return (int)e;
+    recurrence_kernel<T><<<dim3(p.heads, p.B), threads, smem, st>>>(p);
+  });
+  MX_DONE(1);
+}
+
+// ---------------------------------------------------------------------------------------------- short convolution
+template <typename T>
+__global__ void __launch_bounds__(256) short_conv_kernel(const ShortConv p) {
+  const int m = blockIdx.x, b = m / p.S, t = m % p.S, back = p.taps - 1;
+  const T *in = reinterpret_cast<const T *>(p.in);
+  const T *w = reinterpret_cast<const T *>(p.w), *bias = reinterpret_cast<const T *>(p.bias);
+  const T *hist = reinterpret_cast<const T *>(p.hist) + (size_t)b * back * p.channels;
+  T *out = reinterpret_cast<T *>(p.out) + (size_t)m * p.channels;
+  for (int ch = threadIdx.x; ch < p.channels; ch += blockDim.x) {
+    float acc = DT<T>::to_f(bias[ch]);
+    for (int jt = 0; jt < p.taps; jt++) {
+      const int tt = t - back + jt;
+      float x = 0.f;
+      if (tt >= 0) x = DT<T>::to_f(in[((size_t)b * p.S + tt) * p.ld + p.col0 + ch]);
+      else if (p.pos0 > 0) x = DT<T>::to_f(hist[(size_t)(back + tt) * p.channels + ch]);
+      acc = fmaf(DT<T>::to_f(w[(size_t)ch * p.taps + jt]), x, acc);
+    }
+    out[ch] = DT<T>::from_f(silu_f(acc));
+  }
+}
+// after the convolution: the history becomes the last taps - 1 inputs up to the end of this step (zeros before position 0)
+template <typename T>
+__global__ void short_conv_hist_kernel(const ShortConv p) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x, back = p.taps - 1;
+  if (idx >= p.B * p.channels) return;
+  const int b = idx / p.channels, ch = idx % p.channels;
+  const T *in = reinterpret_cast<const T *>(p.in);
+  T *hist = reinterpret_cast<T *>(p.hist) + (size_t)b * back * p.channels;
+  for (int jt = 0; jt < back; jt++) {  // ascending: an entry is read (at jt + S) before it is overwritten
+    const int tt = p.S - back + jt;
+    T v = DT<T>::from_f(0.f);
+    if (tt >= 0) v = in[((size_t)b * p.S + tt) * p.ld + p.col0 + ch];
+    else if (p.pos0 > 0) v = hist[(size_t)(jt + p.S) * p.channels + ch];
+    hist[(size_t)jt * p.channels + ch] = v;
+  }
+}
+int short_conv(cudaStream_t st, int dtype, const ShortConv &p, uint64_t *launches) {
+  MX_DISPATCH(dtype, {
+    short_conv_kernel<T><<<p.B * p.S, 256, 0, st>>>(p);
+    if (p.taps > 1) short_conv_hist_kernel<T><<<(p.B * p.channels + 255) / 256, 256, 0, st>>>(p);
+  });
+  MX_DONE(p.taps > 1 ? 2 : 1);
+}
+
+// ---------------------------------------------------------------------------------------------- gated unit norm
+template <typename T>
+__global__ void __launch_bounds__(128) gate_norm_kernel(const GateNorm p) {
+  const long warp = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= (long)p.M * p.parts) return;
+  const int m = (int)(warp / p.parts), g = (int)(warp % p.parts), len = p.n / p.parts, c0 = g * len;
+  const float *o = p.o + (size_t)m * p.n + c0;
+  const T *gate = reinterpret_cast<const T *>(p.gate) + (size_t)m * p.ldg + c0;
+  const T *w = p.w ? reinterpret_cast<const T *>(p.w) + c0 : nullptr;
+  T *out = reinterpret_cast<T *>(p.out) + (size_t)m * p.n + c0;
+  float ss = 0.f;
+  for (int i = lane; i < len; i += 32) {
+    const float v = p.gate_first ? o[i] * silu_f(DT<T>::to_f(gate[i])) : o[i];
+    ss = fmaf(v, v, ss);
+  }
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / (float)len + p.eps);
+  for (int i = lane; i < len; i += 32) {
+    const float gs = silu_f(DT<T>::to_f(gate[i]));
+    float v = (p.gate_first ? o[i] * gs : o[i]) * inv;
+    if (w) v *= DT<T>::to_f(w[i]);
+    if (!p.gate_first) v *= gs;
+    out[i] = DT<T>::from_f(v);
+  }
+}
+int gate_norm(cudaStream_t st, int dtype, const GateNorm &p, uint64_t *launches) {
+  if (p.parts < 1 || p.n % p.parts) return (int)cudaErrorInvalidValue;
+  const long warps = (long)p.M * p.parts;
+  MX_DISPATCH(dtype, (gate_norm_kernel<T><<<(unsigned)((warps + 3) / 4), 128, 0, st>>>(p)));
+  MX_DONE(1);
+}
+
+// ---------------------------------------------------------------------------------------------- router
+constexpr int MOE_MAX_SLOTS = 8;  // experts + identity <= 256
+template <typename T>
+__global__ void __launch_bounds__(128) moe_router_kernel(const MoePlan p) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= p.M) return;
+  const int m = warp, E = p.experts + p.identity;
+  const T *h = reinterpret_cast<const T *>(p.h) + (size_t)m * p.W;
+  const T *Wr = reinterpret_cast<const T *>(p.router), *corr = reinterpret_cast<const T *>(p.correction);
+  float z[MOE_MAX_SLOTS];
+#pragma unroll
+  for (int sI = 0; sI < MOE_MAX_SLOTS; sI++) z[sI] = -INFINITY;
+  for (int e = 0; e < E; e++) {
+    const T *wr = Wr + (size_t)e * p.W;
+    float d = 0.f;
+    for (int i = lane; i < p.W; i += 32) d = fmaf(DT<T>::to_f(h[i]), DT<T>::to_f(wr[i]), d);
+    d = warp_sum(d);
+#pragma unroll
+    for (int sI = 0; sI < MOE_MAX_SLOTS; sI++)
+      if (e == lane + 32 * sI) z[sI] = d;
+  }
+  float mx = -INFINITY;
+#pragma unroll
+  for (int sI = 0; sI < MOE_MAX_SLOTS; sI++) mx = fmaxf(mx, z[sI]);
+  mx = warp_max(mx);
+  float sum = 0.f, sc[MOE_MAX_SLOTS], ch[MOE_MAX_SLOTS];
+#pragma unroll
+  for (int sI = 0; sI < MOE_MAX_SLOTS; sI++) {
+    sc[sI] = lane + 32 * sI < E ? expf(z[sI] - mx) : 0.f;
+    sum += sc[sI];
+  }
+  sum = warp_sum(sum);
+#pragma unroll
+  for (int sI = 0; sI < MOE_MAX_SLOTS; sI++) {
+    const int e = lane + 32 * sI;
+    sc[sI] = sc[sI] / sum;
+    ch[sI] = e < E ? sc[sI] + DT<T>::to_f(corr[e]) : -INFINITY;
+  }
+  float wsum = 0.f, mine = 0.f;  // lane k keeps the score of the k-th choice
+  int mine_id = 0;
+  for (int k = 0; k < p.top; k++) {
+    float best = -INFINITY, bs = 0.f;
+    int bi = 0x7fffffff;
+#pragma unroll
+    for (int sI = 0; sI < MOE_MAX_SLOTS; sI++)
+      if (ch[sI] > best) { best = ch[sI]; bi = lane + 32 * sI; bs = sc[sI]; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o), os = __shfl_xor_sync(0xffffffffu, bs, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; bs = os; }
+    }
+#pragma unroll
+    for (int sI = 0; sI < MOE_MAX_SLOTS; sI++)
+      if (bi == lane + 32 * sI) ch[sI] = -INFINITY;
+    wsum += bs;
+    if (lane == k) { mine = bs; mine_id = bi; }
+  }
+  if (lane < p.top) {
+    p.ids[(size_t)m * p.top + lane] = mine_id;
+    p.wts[(size_t)m * p.top + lane] = mine / (wsum + 1e-20f) * p.scale;
+  }
+  if (p.shared_gate) {
+    const T *sg = reinterpret_cast<const T *>(p.shared_gate);
+    float d = 0.f;
+    for (int i = lane; i < p.W; i += 32) d = fmaf(DT<T>::to_f(h[i]), DT<T>::to_f(sg[i]), d);
+    d = warp_sum(d);
+    if (lane == 0) p.sgate[m] = 1.0f / (1.0f + expf(-d));
+  }
+}
+__global__ void moe_count_kernel(const int *ids, int n, int experts, int *counts) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n && ids[i] < experts) atomicAdd(&counts[ids[i]], 1);
+}
+// one thread: tiles of every expert's group; counts[e] becomes the group's first sorted position (the scatter's cursor)
+__global__ void moe_tiles_kernel(const MoePlan p) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  int row = 0, nt = 0;
+  for (int e = 0; e < p.experts; e++) {
+    const int cnt = p.counts[e];
+    p.counts[e] = row;
+    for (int r = 0; r < cnt && nt < p.max_tiles; r += p.tile) {
+      p.tile_expert[nt] = e;
+      p.tile_row0[nt] = row + r;
+      p.tile_rows[nt] = min(p.tile, cnt - r);
+      nt++;
+    }
+    row += cnt;
+  }
+  *p.n_tiles = nt;
+}
+__global__ void moe_scatter_kernel(const int *ids, int n, int experts, int *cursor, int *perm) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n && ids[i] < experts) perm[atomicAdd(&cursor[ids[i]], 1)] = i;
+}
+int moe_route(cudaStream_t st, int dtype, const MoePlan &p, uint64_t *launches) {
+  if (p.experts + p.identity > 32 * MOE_MAX_SLOTS || p.top > 32 || p.top < 1 || p.top > p.experts + p.identity) return (int)cudaErrorInvalidValue;
+  MX_DISPATCH(dtype, (moe_router_kernel<T><<<(p.M + 3) / 4, 128, 0, st>>>(p)));
+  int n = 1;
+  if (p.experts > 0) {
+    cudaMemsetAsync(p.counts, 0, sizeof(int) * (p.experts + 1), st);
+    const int ne = p.M * p.top;
+    moe_count_kernel<<<(ne + 255) / 256, 256, 0, st>>>(p.ids, ne, p.experts, p.counts);
+    moe_tiles_kernel<<<1, 32, 0, st>>>(p);
+    moe_scatter_kernel<<<(ne + 255) / 256, 256, 0, st>>>(p.ids, ne, p.experts, p.counts, p.perm);
+    n += 3;
+  }
+  MX_DONE(n);
+}
+
+// ---------------------------------------------------------------------------------------------- experts
+// Tiles of up to `tile` (= 64) sorted rows that share an expert.  PHASE 0: act = f(Wg h) * (Wu h) into the sorted scratch;
+// PHASE 1: y[m * top + slot] = weight * (Wd act).
+constexpr int ME_BM = 64, ME_BN = 64, ME_BK = 16;
+__device__ __forceinline__ float act_f(float g, int kind) {
+  if (kind) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * g * (1.0f + 0.044715f * g * g)));
+  return silu_f(g);
+}
+template <typename T, int PHASE>
+__global__ void __launch_bounds__(256) moe_expert_kernel(const MoeExperts p) {
+  const int tl = blockIdx.y;
+  if (tl >= *p.n_tiles) return;
+  __shared__ float As[ME_BK][ME_BM + 4];
+  __shared__ float Ws[ME_BK][ME_BN + 4];
+  __shared__ float Us[PHASE == 0 ? ME_BK : 1][ME_BN + 4];
+  __shared__ int src[ME_BM];
+  const int e = p.tile_expert[tl], row0 = p.tile_row0[tl], rows = p.tile_rows[tl];
+  const int K = PHASE == 0 ? p.W : p.ff, N = PHASE == 0 ? p.ff : p.W;
+  for (int r = threadIdx.x; r < ME_BM; r += 256) src[r] = r < rows ? p.perm[row0 + r] : -1;
+  __syncthreads();
+  const T *A = PHASE == 0 ? reinterpret_cast<const T *>(p.h) : reinterpret_cast<const T *>(p.act);
+  const T *Wa = PHASE == 0 ? reinterpret_cast<const T *>(p.wg) + (size_t)e * p.ff * p.W : reinterpret_cast<const T *>(p.wd) + (size_t)e * p.W * p.ff;
+  const T *Wb = reinterpret_cast<const T *>(p.wu) + (size_t)e * p.ff * p.W;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4, n0 = blockIdx.x * ME_BN;
+  float acc[4][4] = {}, acu[4][4] = {};
+  for (int k0 = 0; k0 < K; k0 += ME_BK) {
+    for (int i = threadIdx.x; i < ME_BM * ME_BK; i += 256) {
+      const int r = i / ME_BK, c = i % ME_BK;
+      float a = 0.f;
+      if (r < rows && k0 + c < K) {
+        const size_t arow = PHASE == 0 ? (size_t)(src[r] / p.top) : (size_t)(row0 + r);
+        a = DT<T>::to_f(A[arow * K + k0 + c]);
+      }
+      As[c][r] = a;
+      const bool ok = n0 + r < N && k0 + c < K;
+      Ws[c][r] = ok ? DT<T>::to_f(Wa[(size_t)(n0 + r) * K + k0 + c]) : 0.f;
+      if (PHASE == 0) Us[c][r] = ok ? DT<T>::to_f(Wb[(size_t)(n0 + r) * K + k0 + c]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < ME_BK; k++) {
+      float av[4], wv[4], uv[4];
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        av[i] = As[k][ty * 4 + i];
+        wv[i] = Ws[k][tx * 4 + i];
+        uv[i] = PHASE == 0 ? Us[k][tx * 4 + i] : 0.f;
+      }
+#pragma unroll
+      for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+          if (PHASE == 0) acu[i][j] = fmaf(av[i], uv[j], acu[i][j]);
+        }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const int r = ty * 4 + i;
+    if (r >= rows) continue;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const int n = n0 + tx * 4 + j;
+      if (n >= N) continue;
+      if (PHASE == 0) {
+        const float g = rnd<T>(act_f(rnd<T>(acc[i][j]), p.act_kind));
+        reinterpret_cast<T *>(p.act)[(size_t)(row0 + r) * p.ff + n] = DT<T>::from_f(g * rnd<T>(acu[i][j]));
+      } else {
+        p.y[(size_t)src[r] * p.W + n] = p.wts[src[r]] * acc[i][j];
+      }
+    }
+  }
+}
+int moe_experts(cudaStream_t st, int dtype, const MoeExperts &p, uint64_t *launches) {
+  if (p.tile != ME_BM) return (int)cudaErrorInvalidValue;
+  MX_DISPATCH(dtype, {
+    moe_expert_kernel<T, 0><<<dim3((p.ff + ME_BN - 1) / ME_BN, p.max_tiles), 256, 0, st>>>(p);
+    moe_expert_kernel<T, 1><<<dim3((p.W + ME_BN - 1) / ME_BN, p.max_tiles), 256, 0, st>>>(p);
+  });
+  MX_DONE(2);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) moe_combine_kernel(const MoeCombine p) {
+  const int m = blockIdx.x;
+  const T *h = reinterpret_cast<const T *>(p.h) + (size_t)m * p.W;
+  for (int i = threadIdx.x; i < p.W; i += blockDim.x) {
+    float s = 0.f;
+    for (int k = 0; k < p.top; k++) {
+      const int e = p.ids[(size_t)m * p.top + k];
+      s += e < p.experts ? p.y[((size_t)m * p.top + k) * p.W + i] : p.wts[(size_t)m * p.top + k] * DT<T>::to_f(h[i]);
+    }
+    p.x_out[(size_t)m * p.W + i] = p.x[(size_t)m * p.W + i] + s;
+  }
+}
+int moe_combine(cudaStream_t st, int dtype, const MoeCombine &p, uint64_t *launches) {
+  MX_DISPATCH(dtype, (moe_combine_kernel<T><<<p.M, 256, 0, st>>>(p)));
+  MX_DONE(1);
+}
+
+// ---------------------------------------------------------------------------------------------- stream injection
+template <typename T>
+__global__ void __launch_bounds__(256) stream_inject_kernel(float *x, const float *x0, const T *vec, int W) {
+  const size_t m = blockIdx.x;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    float v = x[m * W + i];
+    if (x0) v += x0[m * W + i];
+    x[m * W + i] = v + DT<T>::to_f(vec[i]);
+  }
+}
+int stream_inject(cudaStream_t st, int dtype, float *x, const float *x0, const void *vec, int M, int W, uint64_t *launches) {
+  MX_DISPATCH(dtype, (stream_inject_kernel<T><<<M, 256, 0, st>>>(x, x0, reinterpret_cast<const T *>(vec), W)));
+  MX_DONE(1);
+}
+
+}  // namespace mx
+}  // namespace cake

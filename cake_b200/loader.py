@@ -304,6 +304,47 @@ def listed_block_tensors(vb, cfg: Config, index: int) -> Dict[str, Optional[torc
     return out
 
 
+def mixer_block_tensors(vb, cfg: Config, index: int) -> Dict[str, object]:
+    """The tensors of layer ``index`` of a mixer-list (Setodra) checkpoint by the field names of ``cake_b200_mixer_tensors``
+    (``e_gate`` / ``e_up`` / ``e_down``: lists, one tensor per expert), each checked against the shape its MixerSpec declares.
+    Names under ``l<i>.``: ``norm1``, ``norm2``, ``mix.*`` (the mixer) and ``mlp.*`` (``e<j>.{gate,up,down}``, ``router``,
+    ``correction``, ``shared.{gate,up,down,sg}``)."""
+    sp, H, name = cfg.layers[index], cfg.hidden_size, cfg.layer_name(index)
+
+    def get(short, shape):
+        t = vb.get(f"{name}.{short}")
+        if t is None:
+            raise KeyError(f"tensor {name}.{short} not found")
+        if tuple(t.shape) != tuple(shape):
+            raise ValueError(f"shape mismatch for {name}.{short}, expected: {list(shape)}, got: {list(t.shape)}")
+        return t
+
+    out: Dict[str, object] = {"norm1": get("norm1", (H,)), "o": get("mix.o", (H, sp.inner))}
+    if sp.type == "latent_attention":
+        out.update(q=get("mix.q", (sp.heads * (sp.dim + sp.rot_dim), H)), dkv=get("mix.dkv", (sp.kv_rank + sp.rot_dim, H)),
+                   dkv_norm=get("mix.dkv.norm", (sp.kv_rank,)), uk=get("mix.uk", (sp.heads * sp.dim, sp.kv_rank)),
+                   uv=get("mix.uv", (sp.inner, sp.kv_rank)))
+    elif sp.type == "retention":
+        out.update(q=get("mix.q", (sp.heads * sp.dim, H)), k=get("mix.k", (sp.heads * sp.dim, H)), v=get("mix.v", (sp.inner, H)),
+                   g=get("mix.g", (sp.inner, H)))
+    else:
+        ch = sp.inner + 2 * sp.groups * sp.state
+        out.update({"in": get("mix.in", (2 * sp.inner + 2 * sp.groups * sp.state + sp.heads, H)), "conv": get("mix.conv", (ch, sp.conv)),
+                    "conv_b": get("mix.conv.b", (ch,)), "dt_bias": get("mix.dt_bias", (sp.heads,)), "a_log": get("mix.A_log", (sp.heads,)),
+                    "d": get("mix.D", (sp.heads,)), "norm": get("mix.norm", (sp.inner,))})
+    mo = sp.moe
+    if mo is not None:
+        et = mo.experts + mo.identity
+        out.update(norm2=get("norm2", (H,)), router=get("mlp.router", (et, H)), correction=get("mlp.correction", (et,)),
+                   e_gate=[get(f"mlp.e{j}.gate", (mo.ff, H)) for j in range(mo.experts)],
+                   e_up=[get(f"mlp.e{j}.up", (mo.ff, H)) for j in range(mo.experts)],
+                   e_down=[get(f"mlp.e{j}.down", (H, mo.ff)) for j in range(mo.experts)])
+        if mo.shared_ff:
+            out.update(s_gate=get("mlp.shared.gate", (mo.shared_ff, H)), s_up=get("mlp.shared.up", (mo.shared_ff, H)),
+                       s_down=get("mlp.shared.down", (H, mo.shared_ff)), s_sg=get("mlp.shared.sg", (1, H)))
+    return out
+
+
 def detect_model_prefix(index_path: str, configured: str) -> str:
     """cake/mod.rs:335-357: the text before the first ``.layers.0.`` key of the index wins over the configured prefix."""
     if not os.path.exists(index_path):

@@ -281,8 +281,45 @@ class ListedBlock(B200Transformer):
         return cls(name, h, ctx)
 
 
+class MixerBlock(B200Transformer):
+    """A layer of a mixer-list model (``Config.layers`` of MixerSpec; ``cake_b200_block_load_mixer``): same Forwarder surface
+    and the same ``cake_b200_forward_batch`` call, fp32 activation.  A layer inside a looped range is loaded once and run
+    under one block_idx (cache slot) per pass."""
+
+    @classmethod
+    def load(cls, name: str, ctx: Context) -> "MixerBlock":
+        from .capi import CMixerSpec, CMixerTensors, CMoeSpec, CRotarySpec, MIXER_TENSOR_FIELDS
+        from .config import MIXER_KINDS
+        from .loader import mixer_block_tensors
+        cfg = ctx.config
+        index = [cfg.layer_name(i) for i in range(len(cfg.layers))].index(name)
+        sp = cfg.layers[index]
+        views = mixer_block_tensors(ctx.var_builder, cfg, index)
+        keep, args = [], {}
+        for fld in MIXER_TENSOR_FIELDS:
+            t = views.get(fld)
+            if isinstance(t, list):
+                ts = [x.to(ctx.torch_dtype).contiguous() for x in t]
+                keep.append(ts)
+                args[fld] = ptr_array([ptr(x) for x in ts]) if ts else None
+            else:
+                t = None if t is None else t.to(ctx.torch_dtype).contiguous()
+                keep.append(t)
+                args[fld] = ptr(t)
+        r, mo = sp.rot, sp.moe
+        decay = (ctypes.c_float * max(1, len(sp.decay)))(*sp.decay)
+        spec = CMixerSpec(MIXER_KINDS[sp.type], sp.heads, sp.dim, sp.vdim, sp.rot_dim, sp.kv_rank, sp.scale,
+                          CRotarySpec(r.dims, r.base, r.factor, r.fast, r.slow, r.original),
+                          decay if sp.decay else None, sp.state, sp.groups, sp.conv, sp.norm_groups,
+                          CMoeSpec(mo.experts, mo.identity, mo.top, mo.scale, mo.ff, mo.shared_ff, mo.act) if mo else CMoeSpec())
+        tens = CMixerTensors(**args)
+        h = c_void_p()
+        check(lib().cake_b200_block_load_mixer(ctx.h, index, byref(spec), byref(tens), byref(h)))
+        return cls(name, h, ctx)
+
+
 # Config.block_kind -> the Forwarder that loads and runs its layers
-BLOCK_CLASSES = {"nigenex": ListedBlock}
+BLOCK_CLASSES = {"nigenex": ListedBlock, "setodra": MixerBlock}
 
 
 @dataclass
@@ -326,11 +363,16 @@ class TextModelBase:
         n_emb, n_norm, n_head = cfg.head_tensor_names()
         emb = get(n_emb, (cfg.vocab_size, cfg.hidden_size))
         from .loader import rms_norm_weight
-        lnf = rms_norm_weight(get(n_norm, () if cfg.layer_list else (cfg.hidden_size,)), cfg)   # text_model.rs:186-192
+        lnf = rms_norm_weight(get(n_norm, () if cfg.scalar_final_norm else (cfg.hidden_size,)), cfg)   # text_model.rs:186-192
         head = None if n_head is None else get(n_head, (cfg.vocab_size, cfg.hidden_size))
         check(lib().cake_b200_head_load(ctx.h, ptr(emb), ptr(lnf), ptr(head)))
         blocks: List[Forwarder] = []
-        for i in range(cfg.num_hidden_layers):
+        loaded: Dict[int, Forwarder] = {}   # a layer of a looped range appears once per pass and is loaded once
+        plan = cfg.run_plan() if cfg.layer_list else [(i, None) for i in range(cfg.num_hidden_layers)]
+        for i, _ in plan:
+            if i in loaded:
+                blocks.append(loaded[i])
+                continue
             name = cfg.layer_name(i)
             owner = _topology_owner(ctx.topology, name)
             if owner is None:
@@ -339,7 +381,14 @@ class TextModelBase:
                 if make_remote is None:
                     raise RuntimeError(f"layer {name} is assigned to worker {owner!r} but no transport was given")
                 blocks.append(make_remote(owner, name, ctx))
-        return cls(ctx, blocks, **kw)
+            loaded[i] = blocks[-1]
+        model = cls(ctx, blocks, **kw)
+        # run index -> pass number, for the runs in front of which the stream receives the pass's additions
+        model.injections = {j: t for j, (_, t) in enumerate(plan) if t is not None}
+        if model.injections:
+            steps = get("loop.step", (int(cfg.loop["times"]), cfg.hidden_size))
+            model.loop_steps = [steps[t].contiguous() for t in range(steps.shape[0])]
+        return model
 
     # -- forward (text_model.rs:266-368) ---------------------------------------------------------
     def forward(self, ids, idx: int, want: Optional[Sequence[int]] = None) -> torch.Tensor:
@@ -352,11 +401,19 @@ class TextModelBase:
         x = ctx.empty(b, s, ctx.config.hidden_size, dtype=ctx.stream_dtype)
         check(lib().cake_b200_embed(ctx.h, ids.ctypes.data_as(ctypes.POINTER(c_uint32)), b, s, ptr(x)))
         n, i = len(self.blocks), 0
+        inject = getattr(self, "injections", None) or {}
+        x0 = x if inject else None
+        if inject:
+            with torch.cuda.stream(ctx.torch_stream):
+                x = x0.clone()
         while i < n:
+            if i in inject:  # a pass of a looped range starts: x += (embedding output, from the second pass on) + step vector
+                t = inject[i]
+                check(lib().cake_b200_stream_inject(ctx.h, ptr(x), ptr(x0) if t > 0 else None, ptr(self.loop_steps[t]), t, b * s))
             ident = self.blocks[i].ident()
             j = i
             group = []
-            while j < n and self.blocks[j].ident() == ident:  # contiguous run on the same node (:298-321)
+            while j < n and self.blocks[j].ident() == ident and (j == i or j not in inject):  # contiguous run on the same node (:298-321)
                 group.append((self.blocks[j].layer_name(), idx, j))
                 j += 1
             if ident == "local":

@@ -165,6 +165,76 @@ typedef struct cake_b200_layer_tensors {
 int cake_b200_block_load_spec(cake_b200_ctx *, int layer_idx, const cake_b200_layer_spec *, const cake_b200_layer_tensors *,
                               cake_b200_block **out);
 
+/* ---- mixer-list blocks ----------------------------------------------------------------------------
+ * One layer of a model with cake_b200_config.layer_list whose block is SEQUENTIAL and pre-normed,
+ *     x <- x + mixer(norm1(x));   x <- x + ff(norm2(x))          (RMS norms with [hidden] gains, fp32)
+ * with one of three sequence mixers and an optional routed feed-forward.  Every size and constant is a parameter; a
+ * combination that is not built is refused with CAKE_B200_EINVAL.  Scores, softmax, norms, rotations, recurrent state,
+ * decays, the router and the residual sums are fp32; projections, caches and weights are in D.
+ *   CAKE_B200_MIX_LATENT     attention whose keys and values are expanded from a cached low-rank latent: per head
+ *                            [dim | rot] query entries; dkv h = [kv_rank | rot]: the first part RMS-normed (dkv_norm) is
+ *                            the latent c, the second, rotated, is a key part shared by all heads; keys uk c, values uv c;
+ *                            score = (q . uk c + q_rot . k_rot) * scale, causal softmax.  The cache holds [c | k_rot] only:
+ *                            the query is taken through uk and the weighted latent through uv.
+ *   CAKE_B200_MIX_RETENTION  linear attention with a fixed decay per head, S_t = decay_h S_{t-1} + k_t v_t^T,
+ *                            o_t = S_t^T q_t; q and k rotated, k scaled by dim^-1/2; o of every head divided by its root
+ *                            mean square, times silu(g h), then o.
+ *   CAKE_B200_MIX_STATE_SPACE  `in` h = [z | x | B | C | dt] (inner = heads * vdim, groups * state each for B and C, heads);
+ *                            x, B, C pass a causal convolution per channel (conv [channels, taps], last tap = the current
+ *                            token) + silu; dt <- softplus(dt + dt_bias); S_t = exp(-exp(a_log_h) dt) S_{t-1} + dt B_t x_t^T,
+ *                            y_t = S_t^T C_t + d_h x_t (head h reads group h / (heads / groups)); y * silu(z), RMS-normed in
+ *                            norm_groups equal parts, times norm, then o.
+ * The rotation pairs entry i with i + dims / 2 over the first `dims` entries of a head (the rotated part, for the latent
+ * mixer): angle = position * f_i, f_i = base^(-2i/dims); with yarn_factor > 0 the frequency is blended towards f_i / factor
+ * by a linear ramp between the pair indices that complete `yarn_fast` and `yarn_slow` turns over `yarn_original` positions,
+ * and cos / sin are multiplied by 0.1 ln(factor) + 1.  Tables are computed in double precision at load.
+ * Recurrent state (fp32) and the convolution's last taps - 1 inputs live in the cache, per block_idx: a block that is run
+ * several times per token (a looped range of layers) is given one block_idx per run.
+ * The feed-forward (moe.experts + moe.identity > 0): router logits router h in fp32, s = softmax over all experts; the `top`
+ * largest s + correction are chosen; their weights are s / (sum of the chosen s + 1e-20) * scale.  Experts [0, experts) are
+ * down(act(gate h) * (up h)); the last `identity` router outputs return h itself.  shared_ff > 0: one more expert of that
+ * width runs for every token, times sigmoid(s_sg . h). */
+#define CAKE_B200_MIX_LATENT 1
+#define CAKE_B200_MIX_RETENTION 2
+#define CAKE_B200_MIX_STATE_SPACE 3
+typedef struct cake_b200_rotary_spec {
+  int dims;            /* 0 = no rotation */
+  double base;
+  double yarn_factor;  /* 0 = plain */
+  double yarn_fast, yarn_slow;
+  int yarn_original;
+} cake_b200_rotary_spec;
+typedef struct cake_b200_moe_spec {
+  int experts, identity, top;
+  float scale;
+  int ff, shared_ff;
+  int act;             /* 0 silu, 1 tanh-gelu */
+} cake_b200_moe_spec;
+typedef struct cake_b200_mixer_spec {
+  int kind;
+  int heads, dim, vdim;
+  int rot_dim, kv_rank;   /* latent */
+  float scale;            /* latent */
+  cake_b200_rotary_spec rot;
+  const float *decay;     /* retention: [heads], host */
+  int state, groups, conv, norm_groups;  /* state space; dim is ignored (state is the key size) */
+  cake_b200_moe_spec moe;
+} cake_b200_mixer_spec;
+typedef struct cake_b200_mixer_tensors {
+  const void *norm1, *norm2;                 /* [hidden]; norm2 NULL without a feed-forward */
+  const void *q, *k, *v, *g, *o;             /* retention: all; latent: q [heads*(dim+rot_dim), hidden] and o */
+  const void *dkv, *dkv_norm, *uk, *uv;      /* latent: [kv_rank+rot_dim, hidden], [kv_rank], [heads*dim, kv_rank], [heads*vdim, kv_rank] */
+  const void *in, *conv, *conv_b, *dt_bias, *a_log, *d, *norm;  /* state space */
+  const void *router, *correction;           /* [experts+identity, hidden], [experts+identity] */
+  const void *const *e_gate, *const *e_up, *const *e_down;  /* `experts` pointers each: [ff, hidden] x2, [hidden, ff] */
+  const void *s_gate, *s_up, *s_down, *s_sg; /* shared expert; s_sg [hidden] */
+} cake_b200_mixer_tensors;
+int cake_b200_block_load_mixer(cake_b200_ctx *, int layer_idx, const cake_b200_mixer_spec *, const cake_b200_mixer_tensors *,
+                               cake_b200_block **out);
+/* Between blocks of a looped range: x <- x + (x0 ? x0 : 0) + vec, rows of [hidden] fp32; vec [hidden] in D, host or device
+ * memory on the first call with that pointer (it is uploaded once and kept by the ctx under `slot`, 0 <= slot < 64). */
+int cake_b200_stream_inject(cake_b200_ctx *, float *x_dev, const float *x0_dev, const void *vec, int slot, int rows);
+
 /* ---- cache ------------------------------------------------------------------------------------ */
 int cake_b200_cache_create(cake_b200_ctx *, int batch, int max_seq, cake_b200_cache **out);
 int cake_b200_cache_clear(cake_b200_cache *);
