@@ -302,6 +302,8 @@ class MixerBlock(B200Transformer):
                 ts = [x.to(ctx.torch_dtype).contiguous() for x in t]
                 keep.append(ts)
                 args[fld] = ptr_array([ptr(x) for x in ts]) if ts else None
+            elif fld.startswith("e_"):
+                args[fld] = None
             else:
                 t = None if t is None else t.to(ctx.torch_dtype).contiguous()
                 keep.append(t)

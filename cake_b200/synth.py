@@ -175,3 +175,52 @@ def make_listed_checkpoint(cfg: Config, dtype: str = "bf16", seed: int = 1234, d
         if sp.ff:
             sd[f"{p}.mlp.gate"], sd[f"{p}.mlp.up"], sd[f"{p}.mlp.down"] = rn(sp.ff, H), rn(sp.ff, H), rn(H, sp.ff)
     return sd
+
+
+def make_mixer_checkpoint(cfg: Config, dtype: str = "bf16", seed: int = 1234, device="cpu", std: float = 0.05, router_std: float = 0.5) -> dict:
+    """Random weights of a mixer-list (Setodra) model under the names its checkpoints use: ``embed``, ``head``, ``final.norm``
+    [width], ``loop.step`` [times, width] when the config loops, and per layer ``l<i>.norm1``, ``l<i>.mix.*`` (latent attention:
+    q, dkv, dkv.norm, uk, uv, o; retention: q, k, v, g, o; state space: in, conv, conv.b, dt_bias, A_log, D, norm, o) and, with a
+    feed-forward, ``l<i>.norm2``, ``l<i>.mlp.{router, correction, e<j>.{gate,up,down}, shared.{gate,up,down,sg}}``."""
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed * 1000003 + 77377)
+    td, H = TORCH_DTYPES[dtype], cfg.hidden_size
+
+    def rn(*shape, s=std):
+        return (torch.randn(shape, generator=gen, device=device, dtype=torch.float32) * s).to(td)
+
+    def ru(*shape, lo=0.0, hi=1.0):
+        return (torch.rand(shape, generator=gen, device=device, dtype=torch.float32) * (hi - lo) + lo).to(td)
+
+    sd = {"embed": rn(cfg.vocab_size, H, s=1.0), "head": rn(cfg.vocab_size, H, s=4.0 * std), "final.norm": ru(H, lo=0.8, hi=1.2)}
+    if cfg.loop:
+        sd["loop.step"] = rn(int(cfg.loop["times"]), H, s=0.5)
+    for i, sp in enumerate(cfg.layers):
+        p = cfg.layer_name(i)
+        sd[f"{p}.norm1"] = ru(H, lo=0.8, hi=1.2)
+        sd[f"{p}.mix.o"] = rn(H, sp.inner)
+        if sp.type == "latent_attention":
+            sd[f"{p}.mix.q"] = rn(sp.heads * (sp.dim + sp.rot_dim), H, s=4 * std)
+            sd[f"{p}.mix.dkv"] = rn(sp.kv_rank + sp.rot_dim, H, s=4 * std)
+            sd[f"{p}.mix.dkv.norm"] = ru(sp.kv_rank, lo=0.8, hi=1.2)
+            sd[f"{p}.mix.uk"], sd[f"{p}.mix.uv"] = rn(sp.heads * sp.dim, sp.kv_rank, s=4 * std), rn(sp.inner, sp.kv_rank, s=2 * std)
+        elif sp.type == "retention":
+            sd[f"{p}.mix.q"], sd[f"{p}.mix.k"] = rn(sp.heads * sp.dim, H, s=2 * std), rn(sp.heads * sp.dim, H, s=2 * std)
+            sd[f"{p}.mix.v"], sd[f"{p}.mix.g"] = rn(sp.inner, H, s=2 * std), rn(sp.inner, H, s=2 * std)
+        else:
+            ch = sp.inner + 2 * sp.groups * sp.state
+            sd[f"{p}.mix.in"] = rn(2 * sp.inner + 2 * sp.groups * sp.state + sp.heads, H, s=2 * std)
+            sd[f"{p}.mix.conv"], sd[f"{p}.mix.conv.b"] = rn(ch, sp.conv, s=0.4), rn(ch, s=0.1)
+            sd[f"{p}.mix.dt_bias"], sd[f"{p}.mix.A_log"] = ru(sp.heads, lo=-3.0, hi=0.5), ru(sp.heads, lo=-1.5, hi=1.0)
+            sd[f"{p}.mix.D"], sd[f"{p}.mix.norm"] = ru(sp.heads, lo=0.5, hi=1.5), ru(sp.inner, lo=0.8, hi=1.2)
+        mo = sp.moe
+        if mo is not None:
+            et = mo.experts + mo.identity
+            sd[f"{p}.norm2"] = ru(H, lo=0.8, hi=1.2)
+            sd[f"{p}.mlp.router"], sd[f"{p}.mlp.correction"] = rn(et, H, s=router_std), rn(et, s=0.05)
+            for j in range(mo.experts):
+                sd[f"{p}.mlp.e{j}.gate"], sd[f"{p}.mlp.e{j}.up"], sd[f"{p}.mlp.e{j}.down"] = rn(mo.ff, H, s=2 * std), rn(mo.ff, H, s=2 * std), rn(H, mo.ff, s=2 * std)
+            if mo.shared_ff:
+                sd[f"{p}.mlp.shared.gate"], sd[f"{p}.mlp.shared.up"] = rn(mo.shared_ff, H, s=2 * std), rn(mo.shared_ff, H, s=2 * std)
+                sd[f"{p}.mlp.shared.down"], sd[f"{p}.mlp.shared.sg"] = rn(H, mo.shared_ff, s=2 * std), rn(1, H, s=4 * std)
+    return sd

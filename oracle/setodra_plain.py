@@ -47,6 +47,8 @@ def rope_frequencies(rot, dt=torch.float64):
 
 def rotate(v, rot, pos0=0):
     """v [S, H, D]: the first rot.dims entries of every head are rotated pairwise (i with i + dims/2) by pos * f_i."""
+    if not rot or not int(rot["dims"]):
+        return v
     dims = int(rot["dims"])
     f, amp = rope_frequencies(rot, torch.float64)
     p = torch.arange(pos0, pos0 + v.shape[0], dtype=torch.float64)

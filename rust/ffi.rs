@@ -104,6 +104,79 @@ extern "C" {
         tensors: *const cake_b200_layer_tensors, out: *mut *mut cake_b200_block) -> c_int;
     pub fn cake_b200_logits_rows(ctx: *mut cake_b200_ctx, x_dev: *const c_void, n_rows_total: c_int, rows_host: *const c_int, n: c_int,
         logits_f32_dev: *mut f32) -> c_int;
+    pub fn cake_b200_block_load_mixer(ctx: *mut cake_b200_ctx, layer_idx: c_int, spec: *const cake_b200_mixer_spec,
+        tensors: *const cake_b200_mixer_tensors, out: *mut *mut cake_b200_block) -> c_int;
+    pub fn cake_b200_stream_inject(ctx: *mut cake_b200_ctx, x_dev: *mut f32, x0_dev: *const f32, vec: *const c_void, slot: c_int,
+        rows: c_int) -> c_int;
+}
+
+/// `cake_b200_rotary_spec`, `cake_b200_moe_spec`, `cake_b200_mixer_spec`, `cake_b200_mixer_tensors` (include/cake_b200.h): a
+/// sequential pre-norm block with a latent-attention, retention or state-space mixer and a routed feed-forward.
+#[repr(C)]
+pub struct cake_b200_rotary_spec {
+    pub dims: c_int,
+    pub base: f64,
+    pub yarn_factor: f64,
+    pub yarn_fast: f64,
+    pub yarn_slow: f64,
+    pub yarn_original: c_int,
+}
+#[repr(C)]
+pub struct cake_b200_moe_spec {
+    pub experts: c_int,
+    pub identity: c_int,
+    pub top: c_int,
+    pub scale: f32,
+    pub ff: c_int,
+    pub shared_ff: c_int,
+    pub act: c_int,
+}
+#[repr(C)]
+pub struct cake_b200_mixer_spec {
+    pub kind: c_int,
+    pub heads: c_int,
+    pub dim: c_int,
+    pub vdim: c_int,
+    pub rot_dim: c_int,
+    pub kv_rank: c_int,
+    pub scale: f32,
+    pub rot: cake_b200_rotary_spec,
+    pub decay: *const f32,
+    pub state: c_int,
+    pub groups: c_int,
+    pub conv: c_int,
+    pub norm_groups: c_int,
+    pub moe: cake_b200_moe_spec,
+}
+#[repr(C)]
+pub struct cake_b200_mixer_tensors {
+    pub norm1: *const c_void,
+    pub norm2: *const c_void,
+    pub q: *const c_void,
+    pub k: *const c_void,
+    pub v: *const c_void,
+    pub g: *const c_void,
+    pub o: *const c_void,
+    pub dkv: *const c_void,
+    pub dkv_norm: *const c_void,
+    pub uk: *const c_void,
+    pub uv: *const c_void,
+    pub r#in: *const c_void,
+    pub conv: *const c_void,
+    pub conv_b: *const c_void,
+    pub dt_bias: *const c_void,
+    pub a_log: *const c_void,
+    pub d: *const c_void,
+    pub norm: *const c_void,
+    pub router: *const c_void,
+    pub correction: *const c_void,
+    pub e_gate: *const *const c_void,
+    pub e_up: *const *const c_void,
+    pub e_down: *const *const c_void,
+    pub s_gate: *const c_void,
+    pub s_up: *const c_void,
+    pub s_down: *const c_void,
+    pub s_sg: *const c_void,
 }
 
 /// `cake_b200_block_variant` (include/cake_b200.h): norm placement and per-layer attention mode of the OLMo2 / Gemma3 /
