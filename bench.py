@@ -8,6 +8,7 @@ Llama-3-8B bf16, bs=1, 2k context, layers sharded over N GPUs of one box (N=1 ->
     python bench.py --model 70b [--gpus N]                        # BASELINE configs[3] as the main line
     python bench.py --workload prefill                            # BASELINE configs[4] as the main line
     python bench.py --workload nigenex [--sizes 2k,4k,4k-hd64]    # the Nigenex design beside the closest existing block
+    python bench.py --workload setodra [--sizes 1k,2k]            # the Setodra design beside the closest existing model
 
 A "step" is one decoded token: one pass of the hot path (embed -> blocks -> ln_f/lm_head/argmax) at batch 1.
 tok/s follows the reference's definition (master.rs:131-166): prefill excluded.  Prints ONE JSON line (rank 0).
@@ -1010,6 +1011,132 @@ def nigenex_leg(env: Env, sizes=("2k", "4k", "4k-hd64"), n_layers: int = 4, batc
                                    f"decode bs=1 at {ctx_len} context x {steps} steps", "l2": "prefill activations / decode weights exceed L2"},
             "peaks": {"tensor_tflops": pk["tc"], "hbm_gbs": pk["hbm"], "source": pk["src"]}, "sizes": out}
 
+SETODRA_SIZES = {  # layer sizes of real models (random weights): retention / state-space / state-space / latent attention, each with a routed feed-forward
+    "1k": dict(width=1024, ret=dict(heads=8, dim=128, vdim=128), ssd=dict(heads=32, vdim=64, state=128, groups=4, conv=4, norm_groups=4),
+               lat=dict(heads=8, dim=128, rot_dim=64, vdim=128, kv_rank=512), moe=dict(experts=32, identity=2, top=4, ff=704, shared_ff=1408)),
+    "2k": dict(width=2048, ret=dict(heads=16, dim=128, vdim=128), ssd=dict(heads=64, vdim=64, state=128, groups=8, conv=4, norm_groups=8),
+               lat=dict(heads=16, dim=128, rot_dim=64, vdim=128, kv_rank=512), moe=dict(experts=64, identity=2, top=6, ff=1408, shared_ff=2816)),
+}
+
+
+def setodra_leg(env: Env, sizes=("1k", "2k"), batch: int = 4, seq: int = 4096, ctx_len: int = 2048, steps: int = 32, reps: int = 3) -> dict:
+    """`--workload setodra`: the Setodra design (mixer-list blocks: retention, two state-space layers, latent attention, each
+    followed by a routed feed-forward) beside the framework's closest existing model, Nigenex (the other layer-list model
+    with an fp32 residual stream), at equal width, layer count and active feed-forward width per token, both through
+    TextModelBase / forward_batch:
+      prefill   one step of batch x seq tokens from an empty cache through all layers + the head on the last positions
+      decode    bs=1: a ctx_len-token prompt, then `steps` single-token steps (embed -> layers -> head), timed as a whole
+    Device time by CUDA events on the library's stream; activations (prefill) / weights (decode) exceed the 126 MB L2."""
+    import torch
+    from cake_b200.capi import check, lib, ptr
+    from cake_b200.config import Config, LayerSpec, MixerSpec, MoeSpec, RotarySpec
+    from cake_b200.model import Cache, Context, TextModelBase
+    from cake_b200.synth import make_listed_checkpoint, make_mixer_checkpoint
+    pk = peaks()
+    out, launches, vocab = {}, 0, 32768
+    mseq = max(seq, ctx_len + steps + 8)
+    for name in sizes:
+        z = SETODRA_SIZES[name]
+        W, mo = z["width"], MoeSpec(scale=2.5, **z["moe"])
+        row = {"size": z}
+        for arch in ("setodra", "closest"):
+            if arch == "setodra":
+                rot = RotarySpec(dims=z["lat"]["rot_dim"], base=10000.0, factor=8.0, fast=32.0, slow=1.0, original=2048)
+                layers = [MixerSpec(type="retention", decay=[1 - 2.0 ** (-5 - i % 4) for i in range(z["ret"]["heads"])],
+                                    rot=RotarySpec(dims=z["ret"]["dim"], base=10000.0), moe=mo, **z["ret"]),
+                          MixerSpec(type="mamba2", moe=mo, **z["ssd"]), MixerSpec(type="mamba2", moe=mo, **z["ssd"]),
+                          MixerSpec(type="latent_attention", scale=(z["lat"]["dim"] + z["lat"]["rot_dim"]) ** -0.5, rot=rot, moe=mo, **z["lat"])]
+                cfg = Config(hidden_size=W, intermediate_size=0, vocab_size=vocab, num_hidden_layers=len(layers), num_attention_heads=layers[0].heads,
+                             num_key_value_heads=layers[0].heads, rms_norm_eps=1e-6, head_dim=128, max_seq_len=mseq, block_kind="setodra",
+                             layers=layers, model_prefix="", embed_scale=1.0)
+                sd = make_mixer_checkpoint(cfg, "bf16", seed=5, device=env.dev, std=0.02)
+                r, m2, la = z["ret"], z["ssd"], z["lat"]
+                n_in = [2 * r["heads"] * r["dim"] + 2 * r["heads"] * r["vdim"], 2 * m2["heads"] * m2["vdim"] + 2 * m2["groups"] * m2["state"] + m2["heads"],
+                        la["heads"] * (la["dim"] + la["rot_dim"]) + la["kv_rank"] + la["rot_dim"]]
+                inner = [r["heads"] * r["vdim"], m2["heads"] * m2["vdim"], la["heads"] * la["vdim"]]
+                ff_act = mo.top * mo.ff + mo.shared_ff
+                lin = [2.0 * W * (n_in[i] + inner[i]) for i in (0, 1, 1, 2)]
+                lat_up = 2.0 * la["heads"] * la["kv_rank"] * (la["dim"] + la["vdim"])
+                flop_tok = sum(lin) + lat_up + 4 * (2.0 * W * 3 * ff_act + 2.0 * W * (mo.experts + mo.identity))
+                flop_tok += 4.0 * r["heads"] * r["dim"] * r["vdim"] + 2 * 4.0 * m2["heads"] * m2["state"] * m2["vdim"]   # state update + read-out
+                att_flops = lambda S: 2.0 * la["heads"] * (2 * la["kv_rank"] + la["rot_dim"]) * (S * (S + 1) // 2)
+                wbytes = sum(lin) + lat_up + 4 * (2.0 * W * 3 * ff_act)     # 2 bytes per weight read once = its FLOPs per token
+                state_bytes = 8.0 * (r["heads"] * r["dim"] * r["vdim"] + 2 * m2["heads"] * m2["state"] * m2["vdim"]) + 2.0 * ctx_len * (la["kv_rank"] + la["rot_dim"])
+            else:
+                nh = W // 128
+                ffn = mo.top * mo.ff + mo.shared_ff
+                spec = LayerSpec(heads=nh, kv_heads=max(1, nh // 4), head_dim=128, window=1024, scale=128 ** -0.5, softcap=30.0, ff=ffn)
+                cfg = Config(hidden_size=W, intermediate_size=ffn, vocab_size=vocab, num_hidden_layers=4, num_attention_heads=nh,
+                             num_key_value_heads=spec.kv_heads, head_dim=128, max_seq_len=mseq, block_kind="nigenex", layers=[spec] * 4,
+                             logit_softcap=30.0, model_prefix="")
+                sd = make_listed_checkpoint(cfg, "bf16", seed=5, device=env.dev, std=0.02)
+                n_in1 = (nh + spec.kv_heads) * 128 + nh
+                flop_tok = 4 * 2.0 * W * (n_in1 + 3 * ffn + nh * 128)
+                att_flops = lambda S: 4 * 4.0 * nh * 128 * sum(min(i + 1, 1024) for i in range(S))
+                wbytes = flop_tok
+                state_bytes = 4 * 2.0 * spec.kv_heads * 128 * min(1024, ctx_len)
+            ctx = Context(cfg, sd, "bf16", device=env.local, max_seq=mseq)
+            model = TextModelBase.load(ctx)
+            del sd
+            torch.cuda.empty_cache()
+            # ---- prefill
+            ctx.cache = Cache(ctx, batch, seq)
+            ids = torch.randint(0, vocab, (batch, seq), generator=torch.Generator().manual_seed(11)).numpy()
+            times = []
+            for rr in range(reps + 1):
+                ctx.cache.clear()
+                ctx.sync()
+                l0 = ctx.launch_count()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(ctx.torch_stream)
+                logits = model.forward(ids, 0)
+                e1.record(ctx.torch_stream)
+                ctx.sync()
+                if rr > 0:
+                    times.append(e0.elapsed_time(e1))
+                    launches += ctx.launch_count() - l0
+            ms = statistics.median(times)
+            M = batch * seq
+            flops = flop_tok * M + batch * att_flops(seq) + 2.0 * batch * vocab * W
+            pre = {"tok_s": M / (ms / 1e3), "ms": ms, "tflops": flops / (ms * 1e-3) / 1e12,
+                   "frac_of_tensor_peak": flops / (ms * 1e-3) / 1e12 / pk["tc"], "finite": bool(torch.isfinite(logits.float()).all())}
+            # ---- decode
+            ctx.cache = Cache(ctx, 1, mseq)
+            ids1 = torch.randint(0, vocab, (ctx_len + steps + 3,), generator=torch.Generator().manual_seed(3)).tolist()
+            model.forward([ids1[:ctx_len]], 0)
+            pos = ctx_len
+            for _ in range(3):
+                model.forward([[ids1[pos]]], pos)
+                pos += 1
+            ctx.sync()
+            l0 = ctx.launch_count()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(ctx.torch_stream)
+            for _ in range(steps):
+                lg = model.forward([[ids1[pos]]], pos)
+                pos += 1
+            e1.record(ctx.torch_stream)
+            ctx.sync()
+            launches += ctx.launch_count() - l0
+            dms = e0.elapsed_time(e1) / steps
+            dbytes = wbytes + state_bytes + 2.0 * vocab * W
+            dec = {"tok_s": 1e3 / dms, "ms_per_token": dms, "gb_s": dbytes / (dms * 1e-3) / 1e9, "frac_of_hbm_peak": dbytes / (dms * 1e-3) / 1e9 / pk["hbm"],
+                   "launches_per_token": (ctx.launch_count() - l0) / steps, "finite": bool(torch.isfinite(lg.float()).all())}
+            row[arch] = {"prefill": pre, "decode": dec}
+            ctx.close()
+            del model, ctx
+            torch.cuda.empty_cache()
+        row["prefill_ratio"] = row["setodra"]["prefill"]["tok_s"] / row["closest"]["prefill"]["tok_s"]
+        row["decode_ratio"] = row["setodra"]["decode"]["tok_s"] / row["closest"]["decode"]["tok_s"]
+        out[name] = row
+    head = out[sizes[-1]]
+    return {"metric": f"setodra prefill tok/s (4 layers, width {head['size']['width']}, bf16, bs={batch} x {seq})", "value": head["setodra"]["prefill"]["tok_s"],
+            "unit": "tok/s", "ms_per_step": head["setodra"]["prefill"]["ms"], "steps": reps, "warmup": 1, "gpu_launches": int(launches),
+            "config": {"workload": f"Setodra vs Nigenex at equal width, layer count and active feed-forward width, 4 layers, bf16, prefill bs={batch} x {seq}, "
+                                   f"decode bs=1 at {ctx_len} context x {steps} steps", "l2": "prefill activations / decode weights exceed L2"},
+            "peaks": {"tensor_tflops": pk["tc"], "hbm_gbs": pk["hbm"], "source": pk["src"]}, "sizes": out}
+
+
 # ------------------------------------------------------------------------------------------------
 def run_cuda(args):
     env = Env(args)
@@ -1021,6 +1148,16 @@ def run_cuda(args):
             if env.sampler:
                 env.sampler.start()
             line = nigenex_leg(env, sizes=tuple(args.sizes.split(",")), steps=max(4, min(args.steps, 64)))
+            line["clocks"] = env.sampler.stop() if env.sampler else None
+            line.update({"n_gpus": 1, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic"})
+            emit(line)
+        return
+    if args.workload == "setodra":
+        if rank == 0:
+            if env.sampler:
+                env.sampler.start()
+            sizes = tuple((args.sizes if args.sizes != "2k,4k,4k-hd64" else "1k,2k").split(","))
+            line = setodra_leg(env, sizes=sizes, batch=args.pf_batch, seq=args.pf_seq, steps=max(4, min(args.steps, 64)))
             line["clocks"] = env.sampler.stop() if env.sampler else None
             line.update({"n_gpus": 1, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic"})
             emit(line)
@@ -1098,7 +1235,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
     ap.add_argument("--model", default="8b", choices=["8b", "70b"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "nigenex"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "nigenex", "setodra"])
+    ap.add_argument("--pf-batch", type=int, default=4, help="--workload setodra: batch rows of the prefill step")
+    ap.add_argument("--pf-seq", type=int, default=4096, help="--workload setodra: tokens per row of the prefill step")
     ap.add_argument("--sizes", default="2k,4k,4k-hd64", help="--workload nigenex: which of NIGENEX_SIZES to run")
     ap.add_argument("--extras", default="auto", choices=["auto", "none", "all"],
                     help="auto: config0 + config4 at N=1, config3 (70B) at N=8; none: the headline only")

@@ -207,7 +207,7 @@ struct cake_b200_block {
   cake_b200_mixer_spec ms{};
   void *m_dkv_norm = nullptr, *m_uk = nullptr, *m_uv = nullptr;
   void *m_conv = nullptr, *m_conv_b = nullptr, *m_dt_bias = nullptr, *m_a_log = nullptr, *m_d = nullptr, *m_norm = nullptr;
-  void *m_router = nullptr, *m_corr = nullptr, *m_eg = nullptr, *m_eu = nullptr, *m_ed = nullptr, *m_sg = nullptr;
+  void *m_router = nullptr, *m_corr = nullptr, *m_eg = nullptr, *m_ed = nullptr, *m_sg = nullptr;
   float *m_cos = nullptr, *m_sin = nullptr, *m_decay = nullptr;
   int m_rope_rows = 0;
   bool variant() const { return !ln1 || !ln2 || pan || pfn || window >= 0 || !use_rope || ctx->cfg.pre_reshape_qk_norm; }
@@ -735,7 +735,7 @@ extern "C" void cake_b200_block_free(cake_b200_block *b) {
   cudaSetDevice(b->device);
   void *bufs[] = {b->wqkv, b->wo, b->wgu, b->wd, b->ln1, b->ln2, b->bqkv, b->qn, b->kn, b->pan, b->pfn,
                   b->w_in, b->w_out, b->g, b->shift, b->r1, b->r2, b->m_dkv_norm, b->m_uk, b->m_uv, b->m_conv, b->m_conv_b, b->m_dt_bias,
-                  b->m_a_log, b->m_d, b->m_norm, b->m_router, b->m_corr, b->m_eg, b->m_eu, b->m_ed, b->m_sg, b->m_cos, b->m_sin, b->m_decay};
+                  b->m_a_log, b->m_d, b->m_norm, b->m_router, b->m_corr, b->m_eg, b->m_ed, b->m_sg, b->m_cos, b->m_sin, b->m_decay};
   for (void *p : bufs)
     if (p) cudaFree(p);  // cudaFree synchronises with outstanding work
   (void)cudaGetLastError();
@@ -1123,10 +1123,11 @@ static int tmap_init() {
   return CAKE_B200_OK;
 }
 // [rows, K] row-major matrix of D -> 2-D map with a (64 x box_rows) box and 128-byte swizzle
-static int make_tmap(CUtensorMap *m, const void *ptr, uint64_t rows, uint64_t K, int dtype, uint32_t box_rows) {
+// K: the visible columns (the TMA unit zero-fills past them); ld: the row stride in elements when it is not K
+static int make_tmap(CUtensorMap *m, const void *ptr, uint64_t rows, uint64_t K, int dtype, uint32_t box_rows, uint64_t ld = 0) {
   RC(tmap_init());
   const cuuint64_t gdim[2] = {K, rows};
-  const cuuint64_t gstride[1] = {K * 2};
+  const cuuint64_t gstride[1] = {(ld ? ld : K) * 2};
   const cuuint32_t box[2] = {(cuuint32_t)TC_BK, box_rows};
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = g_encode_tiled(m, dtype == CAKE_B200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
@@ -1156,9 +1157,16 @@ static int make_tmap3(CUtensorMap *m, const void *ptr, uint64_t cols, uint64_t r
 static bool tc_gemm_ok(int M, int N, int K) { return M >= 1 && N % TC_BN == 0 && K % TC_BK == 0; }
 
 // C = epi(A[M,K] W[N,K]^T) on the tensor cores (gemm_tc.cuh)
+struct TcExtra {  // optional modes of the tensor-core GEMM (TcParams in gemm_tc.cuh)
+  const int *tile_group = nullptr;  // grouped product: W holds n_groups stacked [N, K] matrices
+  int n_groups = 1;
+  const float *row_scale = nullptr;
+  int b_kwrap = 0, w_cols = 0, w_ld = 0;  // W's k coordinate wraps at b_kwrap; its visible columns / row stride when not K
+  int w_rows = 0;                         // W's visible rows when fewer than N (the rest reads as zeros)
+};
 template <typename T, int EPI>
 static int gemm_tc_T(cake_b200_ctx *c, const void *A, const void *W, const void *bias, const void *res, void *C, int M, int N, int K,
-                     int act = -1, int ldc = 0, float cap = 0.f) {
+                     int act = -1, int ldc = 0, float cap = 0.f, const TcExtra &x = TcExtra{}) {
   // 128 x 256 tiles when N allows and there are enough tiles to fill the chip; CAKE_B200_TC_BN=128 forces the small tile (A/B aid)
   static const int force_bn = []() { const char *e = getenv("CAKE_B200_TC_BN"); return e ? atoi(e) : 0; }();
   const int tiles_m = (M + TC_BM - 1) / TC_BM;
@@ -1166,11 +1174,12 @@ static int gemm_tc_T(cake_b200_ctx *c, const void *A, const void *W, const void 
   const int bn = big ? 256 : 128;
   // pairs of CTAs sharing the W tile by TMA multicast (gemm_tc.cuh MC): needs an even number of 128-row tiles
   static const int no_mc = []() { const char *e = getenv("CAKE_B200_TC_MC"); return (e && e[0] == '0') ? 1 : 0; }();
-  const bool mc = big && !no_mc && M % 256 == 0 && (tiles_m / 2) * (N / 256) >= c->sm_count / 2;
+  const bool mc = big && !no_mc && M % 256 == 0 && (tiles_m / 2) * (N / 256) >= c->sm_count / 2 && !x.tile_group && !x.b_kwrap;
   CUtensorMap ma, mb;
   RC(make_tmap(&ma, A, (uint64_t)M, (uint64_t)K, c->cfg.dtype, TC_BM));
-  RC(make_tmap(&mb, W, (uint64_t)N, (uint64_t)K, c->cfg.dtype, mc ? 128u : (uint32_t)bn));
-  TcParams p{bias, res, C, M, N, K, act >= 0 ? act : (c->cfg.use_gelu_mlp ? 1 : 0), ldc, cap};
+  RC(make_tmap(&mb, W, x.w_rows ? (uint64_t)x.w_rows : (uint64_t)N * x.n_groups, (uint64_t)(x.w_cols ? x.w_cols : K), c->cfg.dtype,
+               mc ? 128u : (uint32_t)bn, (uint64_t)x.w_ld ? (uint64_t)x.w_ld : (uint64_t)K));
+  TcParams p{bias, res, C, M, N, K, act >= 0 ? act : (c->cfg.use_gelu_mlp ? 1 : 0), ldc, cap, x.tile_group, x.row_scale, x.b_kwrap};
   const int tiles = tiles_m * (N / bn);
   dim3 grid(tiles < c->sm_count ? tiles : c->sm_count), block(TC_THREADS);
   if (mc) {
@@ -1432,10 +1441,10 @@ template <typename T> static bool listed_tc(cake_b200_ctx *, int M, int N, int K
 template <> bool listed_tc<float>(cake_b200_ctx *, int, int, int) { return false; }
 template <typename T, int EPI>
 static int listed_gemm_tc(cake_b200_ctx *c, const void *A, const void *W, const void *res, void *C, int M, int N, int K, int act, int ldc,
-                          float cap = 0.f) {
-  return gemm_tc_T<T, EPI>(c, A, W, nullptr, res, C, M, N, K, act, ldc, cap);
+                          float cap = 0.f, const TcExtra &x = TcExtra{}) {
+  return gemm_tc_T<T, EPI>(c, A, W, nullptr, res, C, M, N, K, act, ldc, cap, x);
 }
-#define NO_TC_F32(EPI) template <> int listed_gemm_tc<float, EPI>(cake_b200_ctx *, const void *, const void *, const void *, void *, int, int, int, int, int, float) { return CAKE_B200_EINVAL; }
+#define NO_TC_F32(EPI) template <> int listed_gemm_tc<float, EPI>(cake_b200_ctx *, const void *, const void *, const void *, void *, int, int, int, int, int, float, const TcExtra &) { return CAKE_B200_EINVAL; }
 NO_TC_F32(TCE_PLAIN) NO_TC_F32(TCE_SWIGLU) NO_TC_F32(TCE_RESIDUAL_F32) NO_TC_F32(TCE_SOFTCAP_F32)
 #undef NO_TC_F32
 
@@ -1678,13 +1687,15 @@ extern "C" int cake_b200_block_load_mixer(cake_b200_ctx *c, int layer_idx, const
       RC(upload(c, &b->m_router, t->router, Et * H * es));
       RC(upload(c, &b->m_corr, t->correction, Et * es));
       if (E) {
-        CU(cudaMalloc(&b->m_eg, E * I * H * es + 16));
-        CU(cudaMalloc(&b->m_eu, E * I * H * es + 16));
+        // all experts stacked: gate / up row-interleaved per expert (as the dense blocks lay theirs out) and the down matrices,
+        // so that a grouped product addresses expert e at row e * N of one matrix
+        CU(cudaMalloc(&b->m_eg, E * 2 * I * H * es + 16));
         CU(cudaMalloc(&b->m_ed, E * H * I * es + 16));
         for (size_t e = 0; e < E; e++) {
           if (!t->e_gate[e] || !t->e_up[e] || !t->e_down[e]) return fail(CAKE_B200_EINVAL, "layer %d: expert %zu has a null tensor", layer_idx, e);
-          RC(pipe_copy(c, (char *)b->m_eg + e * I * H * es, I * H * es, t->e_gate[e], I * H * es, I * H * es, 1));
-          RC(pipe_copy(c, (char *)b->m_eu + e * I * H * es, I * H * es, t->e_up[e], I * H * es, I * H * es, 1));
+          char *gu = (char *)b->m_eg + e * 2 * I * H * es;
+          RC(pipe_copy(c, gu, 2 * H * es, t->e_gate[e], H * es, H * es, I));
+          RC(pipe_copy(c, gu + H * es, 2 * H * es, t->e_up[e], H * es, H * es, I));
           RC(pipe_copy(c, (char *)b->m_ed + e * H * I * es, H * I * es, t->e_down[e], H * I * es, H * I * es, 1));
         }
       }
@@ -1706,6 +1717,18 @@ extern "C" int cake_b200_block_load_mixer(cake_b200_ctx *c, int layer_idx, const
   return CAKE_B200_OK;
 }
 
+// Long portions of a latent-attention layer in 16-bit D run as matrix products on the tensor cores when the tiles cover the
+// shapes: scores = qa . cache^T (K = kv_rank + rot_dim), weighted latent = weights . latent (N = kv_rank).
+static bool latent_on_tc(const cake_b200_ctx *c, const cake_b200_block *b) {
+  static const bool no_tc = []() { const char *e = getenv("CAKE_B200_NO_TC"); return e && e[0] == '1'; }();
+  const cake_b200_mixer_spec &sp = b->ms;
+  return !no_tc && c->cfg.dtype != CAKE_B200_F32 && sp.kind == CAKE_B200_MIX_LATENT && (sp.kv_rank + sp.rot_dim) % TC_BK == 0 && sp.kv_rank % TC_BN == 0;
+}
+static int latent_cap_t(int cap) { return (cap + 63) / 64 * 64; }
+constexpr int LATENT_TC_ROWS = 4096;     // (token, head) rows per block of the matrix-product form
+constexpr int LATENT_TC_MIN_ROWS = 1024; // shorter steps take the per-row kernels
+constexpr int LATENT_SPLIT_MAX = 32;
+
 static int cache_ensure_mixer(cake_b200_cache *k, int layer, const cake_b200_block *b) {
   if (layer < 0 || layer >= (int)k->k.size()) return fail(CAKE_B200_EINVAL, "block_idx %d out of range", layer);
   cake_b200_ctx *c = k->ctx;
@@ -1718,6 +1741,8 @@ static int cache_ensure_mixer(cake_b200_cache *k, int layer, const cake_b200_blo
   if (k->kv_heads[layer]) return CAKE_B200_OK;
   if (sp.kind == CAKE_B200_MIX_LATENT) {
     CU(cudaMalloc(&k->k[layer], (size_t)k->batch * k->cap * width * c->es + 16));
+    // the latent once more with the positions innermost, for the matrix-product form of long portions (latent_on_tc)
+    if (latent_on_tc(c, b)) CU(cudaMalloc(&k->v[layer], (size_t)k->batch * sp.kv_rank * latent_cap_t(k->cap) * c->es + 16));
   } else {
     CU(cudaMalloc(&k->rec_state[layer], (size_t)k->batch * width * sizeof(float)));
     if (sp.kind == CAKE_B200_MIX_STATE_SPACE && sp.conv > 1)
@@ -1730,13 +1755,20 @@ static int cache_ensure_mixer(cake_b200_cache *k, int layer, const cake_b200_blo
 
 // scratch of one block for M rows, carved from the ctx arena (base == nullptr: sizes only)
 struct MixerScratch {
-  void *h, *proj, *qa, *lat, *att, *conv, *act, *sact;
-  float *o32, *wts, *sgate, *y;
-  int *ids, *counts, *perm, *tile_expert, *tile_row0, *tile_rows, *n_tiles;
-  int max_tiles;
+  void *h, *proj, *qa, *lat, *att, *conv, *act, *sact, *sorted, *pw;
+  float *o32, *wts, *sgate, *y, *part, *scores;
+  int nsplit, lat_tok;
+  int *ids, *counts, *perm, *pos_of, *tile_expert;
+  int max_tiles, tile;
   size_t total;
 };
-static MixerScratch mixer_scratch(const cake_b200_ctx *c, const cake_b200_block *b, size_t M, char *base) {
+// the routed experts of a block run as grouped products on the tensor cores when D is 16-bit and the tiles cover the shapes
+static bool moe_on_tc(const cake_b200_ctx *c, const cake_b200_block *b) {
+  static const bool no_tc = []() { const char *e = getenv("CAKE_B200_NO_TC"); return e && e[0] == '1'; }();
+  const cake_b200_moe_spec &mo = b->ms.moe;
+  return !no_tc && c->cfg.dtype != CAKE_B200_F32 && mo.experts > 0 && c->cfg.hidden % 128 == 0 && mo.ff % 64 == 0;
+}
+static MixerScratch mixer_scratch(const cake_b200_ctx *c, const cake_b200_block *b, size_t M, char *base, int S = 1, int n_keys = 1) {
   MixerScratch s{};
   size_t off = 0;
   auto take = [&](size_t bytes) -> void * {
@@ -1752,6 +1784,15 @@ static MixerScratch mixer_scratch(const cake_b200_ctx *c, const cake_b200_block 
   if (sp.kind == CAKE_B200_MIX_LATENT) {
     s.qa = take(M * sp.heads * (sp.kv_rank + sp.rot_dim) * es);
     s.lat = take(M * sp.heads * sp.kv_rank * es);
+    if (latent_on_tc(c, b) && (size_t)S * sp.heads >= LATENT_TC_MIN_ROWS) {
+      s.lat_tok = std::max(1, std::min(S, LATENT_TC_ROWS / sp.heads));
+      const size_t rows = (size_t)s.lat_tok * sp.heads, kp = ((size_t)n_keys + TC_BN - 1) / TC_BN * TC_BN;
+      s.scores = (float *)take(rows * kp * sizeof(float));
+      s.pw = take(rows * 2 * kp * es);
+    } else if (M * sp.heads <= 2048 && n_keys > 128) {
+      s.nsplit = std::min(LATENT_SPLIT_MAX, (n_keys + 127) / 128);
+      s.part = (float *)take(M * sp.heads * s.nsplit * (sp.kv_rank + 2) * sizeof(float));
+    }
   } else {
     s.o32 = (float *)take(M * inner * sizeof(float));
     if (sp.kind == CAKE_B200_MIX_STATE_SPACE) s.conv = take(M * (inner + 2 * (size_t)sp.groups * sp.state) * es);
@@ -1759,19 +1800,20 @@ static MixerScratch mixer_scratch(const cake_b200_ctx *c, const cake_b200_block 
   const cake_b200_moe_spec &mo = sp.moe;
   if (mo.experts + mo.identity > 0) {
     const size_t nt = M * mo.top;
-    s.max_tiles = (int)((nt + 63) / 64 + mo.experts);
+    s.tile = moe_on_tc(c, b) ? TC_BM : 64;
+    s.max_tiles = (int)((nt + s.tile - 1) / s.tile + std::min<size_t>(mo.experts, nt));
+    const size_t rows = (size_t)s.max_tiles * s.tile;
     s.ids = (int *)take(nt * sizeof(int));
     s.wts = (float *)take(nt * sizeof(float));
     s.sgate = (float *)take(M * sizeof(float));
     s.counts = (int *)take((mo.experts + 1) * sizeof(int));
-    s.perm = (int *)take(nt * sizeof(int));
+    s.perm = (int *)take(rows * sizeof(int));
+    s.pos_of = (int *)take(nt * sizeof(int));
     s.tile_expert = (int *)take(s.max_tiles * sizeof(int));
-    s.tile_row0 = (int *)take(s.max_tiles * sizeof(int));
-    s.tile_rows = (int *)take(s.max_tiles * sizeof(int));
-    s.n_tiles = (int *)take(sizeof(int));
     if (mo.experts) {
-      s.act = take(nt * mo.ff * es);
-      s.y = (float *)take(nt * H * sizeof(float));
+      s.act = take(rows * mo.ff * es);
+      s.y = (float *)take(rows * H * sizeof(float));
+      if (s.tile == TC_BM) s.sorted = take(rows * H * es);
     }
     if (mo.shared_ff) s.sact = take(M * mo.shared_ff * es);
   }
@@ -1785,7 +1827,7 @@ static int enqueue_mixer_layers(cake_b200_ctx *c, cake_b200_block *const *blocks
   const int H = c->cfg.hidden, M = B * S, dt = c->cfg.dtype;
   size_t need = 0;
   for (int i = 0; i < n; i++) {
-    need = std::max(need, mixer_scratch(c, blocks[i], (size_t)M, nullptr).total);
+    need = std::max(need, mixer_scratch(c, blocks[i], (size_t)M, nullptr, S, pos0 + S).total);
     if (blocks[i]->m_cos && pos0 + S > blocks[i]->m_rope_rows)
       return fail(CAKE_B200_ESTATE, "position %d exceeds the rotation table (%d rows = the ctx's max_seq)", pos0 + S, blocks[i]->m_rope_rows);
   }
@@ -1806,7 +1848,7 @@ static int enqueue_mixer_layers(cake_b200_ctx *c, cake_b200_block *const *blocks
       const cake_b200_block *b = blocks[i];
       const cake_b200_mixer_spec &sp = b->ms;
       const int l = block_idx[i], inner = sp.heads * sp.vdim;
-      const MixerScratch w = mixer_scratch(c, b, (size_t)M, (char *)c->mx_ws);
+      const MixerScratch w = mixer_scratch(c, b, (size_t)M, (char *)c->mx_ws, S, pos0 + S);
       // 1. h = norm1(x); every input projection of the mixer in one product
       RC(launch_pdl(c, norm_shift_rows_kernel<T>, dim3(M), dim3(256), 0, cur, (const int *)nullptr, 1, 0, (const T *)b->ln1, 1, (const T *)nullptr,
                     (const float *)nullptr, (float *)nullptr, (T *)w.h, (T *)nullptr, S, H, c->cfg.rms_eps, pos0));
@@ -1816,14 +1858,38 @@ static int enqueue_mixer_layers(cake_b200_ctx *c, cake_b200_block *const *blocks
       // 2. the mixer: [M, inner] in D
       if (sp.kind == CAKE_B200_MIX_LATENT) {
         const int Dk = sp.kv_rank + sp.rot_dim, qw = sp.dim + sp.rot_dim;
-        mx::LatentPrep lp{w.proj, b->n_in_pad, sp.heads * qw, b->m_dkv_norm, b->m_cos, b->m_sin, sp.rot.dims, kc->k[l], w.qa,
+        const int cap_t = latent_cap_t(kc->cap);
+        mx::LatentPrep lp{w.proj, b->n_in_pad, sp.heads * qw, b->m_dkv_norm, b->m_cos, b->m_sin, sp.rot.dims, kc->k[l], kc->v[l], cap_t, w.qa,
                           B, S, sp.heads, sp.dim, sp.rot_dim, sp.kv_rank, kc->cap, pos0, c->cfg.rms_eps};
         MX(mx::latent_prep(st, dt, lp, lc));
         // the unrotated query through the key expansion: qa[m, h, :rank] = q[m, h, :dim] . uk[h]   (uk[h]: [dim, rank])
         mx::HeadGemm ga{w.proj, b->m_uk, w.qa, M, sp.kv_rank, sp.dim, sp.heads, qw, (long)sp.dim * sp.kv_rank, Dk, b->n_in_pad, sp.kv_rank, sp.heads * Dk, 1};
         MX(mx::head_gemm(st, dt, ga, lc));
-        mx::LatentAttn la{w.qa, kc->k[l], w.lat, B, S, sp.heads, sp.kv_rank, sp.rot_dim, kc->cap, pos0, sp.scale};
-        MX(mx::latent_attention(st, dt, la, lc));
+        if (w.scores && kc->v[l]) {
+          // blocks of lat_tok tokens x heads rows: scores = qa . cache^T on the keys the block's last token sees, softmax with
+          // the causal mask into w_hi | w_lo, lat = [w_hi | w_lo] . latent^T with the latent's k coordinate wrapping at kp
+          for (int bb = 0; bb < B; bb++)
+            for (int t0 = 0; t0 < S; t0 += w.lat_tok) {
+              const int nt = std::min(w.lat_tok, S - t0), rows = nt * sp.heads, nk = pos0 + t0 + nt, kp = round_up(nk, TC_BN);
+              const T *qa_b = (const T *)w.qa + ((size_t)bb * S + t0) * sp.heads * Dk;
+              const T *kc_b = (const T *)kc->k[l] + (size_t)bb * kc->cap * Dk;
+              const T *ct_b = (const T *)kc->v[l] + (size_t)bb * sp.kv_rank * cap_t;
+              TcExtra xs;
+              xs.w_rows = nk;   // rows past the visible keys read as zeros
+              RC((listed_gemm_tc<T, TCE_SOFTCAP_F32>(c, qa_b, kc_b, nullptr, w.scores, rows, kp, Dk, 0, 0, 0.f, xs)));
+              mx::LatentSoftmax sm{w.scores, w.pw, nt, sp.heads, kp, pos0 + t0, sp.scale};
+              MX(mx::latent_softmax(st, dt, sm, lc));
+              TcExtra xv;
+              xv.b_kwrap = kp;
+              xv.w_cols = nk;
+              xv.w_ld = cap_t;
+              RC((listed_gemm_tc<T, TCE_PLAIN>(c, w.pw, ct_b, nullptr, (T *)w.lat + ((size_t)bb * S + t0) * sp.heads * sp.kv_rank, rows, sp.kv_rank,
+                                               2 * kp, 0, 0, 0.f, xv)));
+            }
+        } else {
+          mx::LatentAttn la{w.qa, kc->k[l], w.lat, B, S, sp.heads, sp.kv_rank, sp.rot_dim, kc->cap, pos0, sp.scale, w.part, w.nsplit};
+          MX(mx::latent_attention(st, dt, la, lc));
+        }
         // the weighted latent through the value expansion: att[m, h, :] = uv[h] lat[m, h]   (uv[h]: [vdim, rank])
         mx::HeadGemm gv{w.lat, b->m_uv, w.att, M, sp.vdim, sp.kv_rank, sp.heads, sp.kv_rank, (long)sp.vdim * sp.kv_rank, sp.vdim,
                         sp.heads * sp.kv_rank, sp.kv_rank, inner, 0};
@@ -1859,21 +1925,32 @@ static int enqueue_mixer_layers(cake_b200_ctx *c, cake_b200_block *const *blocks
         RC(launch_pdl(c, norm_shift_rows_kernel<T>, dim3(M), dim3(256), 0, cur, (const int *)nullptr, 1, 0, (const T *)b->ln2, 1, (const T *)nullptr,
                       (const float *)nullptr, (float *)nullptr, (T *)w.h, (T *)nullptr, S, H, c->cfg.rms_eps, pos0));
         mx::MoePlan mp{w.h, b->m_router, b->m_corr, mo.shared_ff ? b->m_sg : nullptr, M, H, mo.experts, mo.identity, mo.top, mo.scale, w.ids, w.wts,
-                       w.sgate, 64, w.counts, w.perm, w.tile_expert, w.tile_row0, w.tile_rows, w.n_tiles, w.max_tiles};
+                       w.sgate, w.tile, w.counts, w.perm, w.pos_of, w.tile_expert, w.max_tiles};
         MX(mx::moe_route(st, dt, mp, lc));
-        if (mo.experts) {
-          mx::MoeExperts me{w.h, b->m_eg, b->m_eu, b->m_ed, w.act, w.y, M, H, mo.ff, mo.top, mo.act, w.perm, w.tile_expert, w.tile_row0, w.tile_rows,
-                            w.n_tiles, w.wts, 64, w.max_tiles};
+        if (mo.experts && w.sorted) {  // grouped products: sorted rows of h -> act(gate) * up -> down, expert e at row e * N of the stacked weights
+          const int rows = w.max_tiles * w.tile;
+          MX(mx::moe_gather(st, dt, w.h, w.perm, w.sorted, rows, H, mo.top, lc));
+          TcExtra xg;
+          xg.tile_group = w.tile_expert;
+          xg.n_groups = mo.experts;
+          RC((listed_gemm_tc<T, TCE_SWIGLU>(c, w.sorted, b->m_eg, nullptr, w.act, rows, 2 * mo.ff, H, mo.act, mo.ff, 0.f, xg)));
+          RC((listed_gemm_tc<T, TCE_SOFTCAP_F32>(c, w.act, b->m_ed, nullptr, w.y, rows, H, mo.ff, 0, 0, 0.f, xg)));
+        } else if (mo.experts) {
+          mx::MoeExperts me{w.h, b->m_eg, b->m_ed, w.act, w.y, M, H, mo.ff, mo.top, mo.act, w.perm, w.tile_expert, w.tile, w.max_tiles};
           MX(mx::moe_experts(st, dt, me, lc));
         }
-        mx::MoeCombine mc{cur, x_out, w.h, w.y, w.wts, w.ids, M, H, mo.top, mo.experts};
+        mx::MoeCombine mc{cur, x_out, w.h, w.y, w.wts, w.ids, w.pos_of, M, H, mo.top, mo.experts};
         MX(mx::moe_combine(st, dt, mc, lc));
         if (mo.shared_ff) {
           RowsGemm gu{w.h, b->wgu, nullptr, w.sact, M, 2 * mo.shared_ff, H, H, mo.shared_ff, mo.act, 0.f};
           if (listed_tc<T>(c, M, 2 * mo.shared_ff, H)) RC((listed_gemm_tc<T, TCE_SWIGLU>(c, w.h, b->wgu, nullptr, w.sact, M, 2 * mo.shared_ff, H, mo.act, mo.shared_ff)));
           else RC((gemm_rows_T<T, RE_GATE_UP>(c, gu)));
           RowsGemm gd{w.sact, b->wd, x_out, x_out, M, H, mo.shared_ff, mo.shared_ff, H, 0, 0.f, w.sgate};
-          RC((gemm_rows_T<T, RE_RESIDUAL_F32>(c, gd)));
+          if (listed_tc<T>(c, M, H, mo.shared_ff) && ((uintptr_t)x_out & 15) == 0) {
+            TcExtra xs;
+            xs.row_scale = w.sgate;
+            RC((listed_gemm_tc<T, TCE_RESIDUAL_F32>(c, w.sact, b->wd, x_out, x_out, M, H, mo.shared_ff, 0, 0, 0.f, xs)));
+          } else RC((gemm_rows_T<T, RE_RESIDUAL_F32>(c, gd)));
         }
       }
     }

@@ -49,6 +49,14 @@ struct TcParams {
   int ldc;  // TCE_SWIGLU: row stride of C in elements when it is a column range of a wider buffer (0 = N/2; a multiple of 8,
             // like the column offset folded into C)
   float cap; // TCE_SOFTCAP_F32
+  // grouped product (a routed feed-forward): the rows of A are sorted by group in blocks of TC_BM rows, tile_group[m0 / TC_BM]
+  // names the group of a row block (< 0: the block is empty and skipped), and group g multiplies by rows g * N .. g * N + N - 1
+  // of W (map_b covers all groups).  nullptr: one group.
+  const int *tile_group = nullptr;
+  // TCE_RESIDUAL_F32: optional [M] fp32, C = residual + row_scale[m] * accumulator (a per-row gate on the product)
+  const float *row_scale = nullptr;
+  // k-block coordinate of W wraps at this many elements (0 = never): A = [P_hi | P_lo] against one copy of W
+  int b_kwrap = 0;
 };
 
 // Tile rasterisation: groups of TC_GM m-tiles (16 x 128 rows = 16 MB of A at K=4096) are walked n-major, so the A
@@ -191,6 +199,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       for (int t = first; t < n_units; t += stride) {
         int m0, n0;
         unit_tile(t, m0, n0);
+        int wrow = n0;
+        if (p.tile_group) {
+          const int g = p.tile_group[m0 / TC_BM];
+          if (g < 0) continue;
+          wrow += g * p.N;
+        }
         for (int kb = 0; kb < kblocks; kb++) {
           mbar_wait(&empty[s], ph ^ 1u);
           unsigned char *st = smem + (size_t)s * TcCfg<BN>::STAGE_BYTES;
@@ -199,7 +213,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           if (MC)  // map_b has a 128-row box here: our half of the W tile, delivered to both CTAs
             tma_load_2d_mc(st + TC_BM * TC_BK * 2 + crank * (128 * TC_BK * 2), &map_b, kb * TC_BK, n0 + (int)crank * 128, &full[s], (uint16_t)3);
           else
-            tma_load_2d(st + TC_BM * TC_BK * 2, &map_b, kb * TC_BK, n0, &full[s]);
+            tma_load_2d(st + TC_BM * TC_BK * 2, &map_b, p.b_kwrap ? (kb * TC_BK) % p.b_kwrap : kb * TC_BK, wrow, &full[s]);
           if (++s == TcCfg<BN>::STAGES) { s = 0; ph ^= 1u; }
         }
       }
@@ -211,9 +225,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       int s = 0;
       uint32_t ph = 0;
       int it = 0;
-      for (int t = first; t < n_units; t += stride, it++) {
+      for (int t = first; t < n_units; t += stride) {
+        if (p.tile_group) {
+          int m0, n0;
+          unit_tile(t, m0, n0);
+          if (p.tile_group[m0 / TC_BM] < 0) continue;
+        }
         const int a = it & 1;
         const uint32_t aph = (uint32_t)(it >> 1) & 1u;
+        it++;
         mbar_wait(&acc_empty[a], aph ^ 1u);  // the epilogue has drained this accumulator
         tc_fence_after();
         const uint32_t tmem_c = tmem_base + (uint32_t)(a * BN);
@@ -239,11 +259,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const T *res = reinterpret_cast<const T *>(p.residual);
     T *C = reinterpret_cast<T *>(p.C);
     int it = 0;
-    for (int t = first; t < n_units; t += stride, it++) {
-      const int a = it & 1;
-      const uint32_t aph = (uint32_t)(it >> 1) & 1u;
+    for (int t = first; t < n_units; t += stride) {
       int m0, n0;
       unit_tile(t, m0, n0);
+      if (p.tile_group && p.tile_group[m0 / TC_BM] < 0) continue;
+      const int a = it & 1;
+      const uint32_t aph = (uint32_t)(it >> 1) & 1u;
+      it++;
       const int row = m0 + wq * 32 + lane;
       mbar_wait(&acc_full[a], aph);
       tc_fence_after();
@@ -285,10 +307,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const float4 *r4 = reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p.residual) + off);
             float4 *dst = reinterpret_cast<float4 *>(reinterpret_cast<float *>(p.C) + off);
 #pragma unroll
+            const float rs = p.row_scale ? p.row_scale[row] : 1.0f;
             for (int j = 0; j < 8; j++) {
               float4 v = r4[j];
-              v.x += __uint_as_float(r[4 * j]); v.y += __uint_as_float(r[4 * j + 1]);
-              v.z += __uint_as_float(r[4 * j + 2]); v.w += __uint_as_float(r[4 * j + 3]);
+              v.x = fmaf(rs, __uint_as_float(r[4 * j]), v.x); v.y = fmaf(rs, __uint_as_float(r[4 * j + 1]), v.y);
+              v.z = fmaf(rs, __uint_as_float(r[4 * j + 2]), v.z); v.w = fmaf(rs, __uint_as_float(r[4 * j + 3]), v.w);
               dst[j] = v;
             }
           } else {

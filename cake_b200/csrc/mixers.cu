@@ -56,7 +56,12 @@ __global__ void __launch_bounds__(128) latent_prep_kernel(const LatentPrep p) {
   const float inv = 1.0f / sqrtf((red[0] + red[1] + red[2] + red[3]) / (float)p.rank + p.eps);
   T *crow = reinterpret_cast<T *>(p.cache) + ((size_t)b * p.cap + pos) * Dk;
   const T *w = reinterpret_cast<const T *>(p.norm_w);
-  for (int i = threadIdx.x; i < p.rank; i += blockDim.x) crow[i] = DT<T>::from_f(DT<T>::to_f(kv[i]) * inv * DT<T>::to_f(w[i]));
+  T *ct = p.cache_t ? reinterpret_cast<T *>(p.cache_t) + (size_t)b * p.rank * p.cap_t + pos : nullptr;
+  for (int i = threadIdx.x; i < p.rank; i += blockDim.x) {
+    const T c = DT<T>::from_f(DT<T>::to_f(kv[i]) * inv * DT<T>::to_f(w[i]));
+    crow[i] = c;
+    if (ct) ct[(size_t)i * p.cap_t] = c;
+  }
   for (int i = threadIdx.x; i < p.rot; i += blockDim.x) crow[p.rank + i] = DT<T>::from_f(rotated<T>(kv + p.rank, i, p.rope_dims, cs, sn));
   T *qa = reinterpret_cast<T *>(p.qa) + (size_t)m * p.heads * Dk;
   for (int i = threadIdx.x; i < p.heads * p.rot; i += blockDim.x) {
@@ -130,9 +135,146 @@ __global__ void __launch_bounds__(128) latent_attn_kernel(const LatentAttn p) {
     if (c < p.rank) out[c] = DT<T>::from_f(acc[i] * il);
   }
 }
+// Steps of a few rows.  CTA (row-head, split): its four warps walk the split's keys four at a time each, their partials are
+// merged in shared memory and written as (max, sum, weighted latent); a second kernel merges the splits.
+template <typename T, int NR>
+__global__ void __launch_bounds__(128) latent_attn_split_kernel(const LatentAttn p) {
+  __shared__ float sm_m[4], sm_l[4];
+  extern __shared__ float sm_acc[];  // [4][rank]
+  const int mh = blockIdx.x, split = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m = mh / p.heads, b = m / p.S, t = m % p.S, n_keys = p.pos0 + t + 1, Dk = p.rank + p.rot;
+  const int per = ((n_keys + p.nsplit - 1) / p.nsplit + 15) / 16 * 16;
+  const int k0 = split * per, k1 = min(n_keys, k0 + per);
+  const T *q = reinterpret_cast<const T *>(p.qa) + (size_t)mh * Dk;
+  const T *kc = reinterpret_cast<const T *>(p.cache) + (size_t)b * p.cap * Dk;
+  float qv[NR], acc[NR];
+#pragma unroll
+  for (int i = 0; i < NR; i++) {
+    const int c = lane + 32 * i;
+    qv[i] = c < Dk ? DT<T>::to_f(q[c]) * p.scale : 0.f;
+    acc[i] = 0.f;
+  }
+  float mx = -INFINITY, l = 0.f;
+  for (int j = k0 + 4 * warp; j < k1; j += 16) {
+    float kv[4][NR], s[4];
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      const bool ok = j + u < k1;
+      const T *row = kc + (size_t)(ok ? j + u : j) * Dk;
+      float part = 0.f;
+#pragma unroll
+      for (int i = 0; i < NR; i++) {
+        const int c = lane + 32 * i;
+        kv[u][i] = c < Dk ? DT<T>::to_f(row[c]) : 0.f;
+        part = fmaf(qv[i], kv[u][i], part);
+      }
+      s[u] = part;
+    }
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      s[u] = warp_sum(s[u]);
+      if (j + u >= k1) s[u] = -INFINITY;
+    }
+    const float mn = fmaxf(fmaxf(mx, fmaxf(s[0], s[1])), fmaxf(s[2], s[3]));
+    const float corr = expf(mx - mn);
+    float pr[4];
+#pragma unroll
+    for (int u = 0; u < 4; u++) pr[u] = expf(s[u] - mn);
+    l = l * corr + ((pr[0] + pr[1]) + (pr[2] + pr[3]));
+#pragma unroll
+    for (int i = 0; i < NR; i++) {
+      float a = acc[i] * corr;
+#pragma unroll
+      for (int u = 0; u < 4; u++) a = fmaf(pr[u], kv[u][i], a);
+      acc[i] = a;
+    }
+    mx = mn;
+  }
+  if (lane == 0) { sm_m[warp] = mx; sm_l[warp] = l; }
+#pragma unroll
+  for (int i = 0; i < NR; i++) {
+    const int c = lane + 32 * i;
+    if (c < p.rank) sm_acc[warp * p.rank + c] = acc[i];
+  }
+  __syncthreads();
+  const float M4 = fmaxf(fmaxf(sm_m[0], sm_m[1]), fmaxf(sm_m[2], sm_m[3]));
+  float f[4], L = 0.f;
+#pragma unroll
+  for (int w = 0; w < 4; w++) {
+    f[w] = sm_m[w] == -INFINITY ? 0.f : expf(sm_m[w] - M4);
+    L = fmaf(sm_l[w], f[w], L);
+  }
+  float *out = p.part + ((size_t)mh * p.nsplit + split) * (p.rank + 2);
+  if (threadIdx.x == 0) { out[0] = M4; out[1] = L; }
+  for (int c = threadIdx.x; c < p.rank; c += blockDim.x)
+    out[2 + c] = (sm_acc[c] * f[0] + sm_acc[p.rank + c] * f[1]) + (sm_acc[2 * p.rank + c] * f[2] + sm_acc[3 * p.rank + c] * f[3]);
+}
+template <typename T>
+__global__ void __launch_bounds__(128) latent_attn_merge_kernel(const LatentAttn p) {
+  const int mh = blockIdx.x;
+  const float *part = p.part + (size_t)mh * p.nsplit * (p.rank + 2);
+  float M = -INFINITY;
+  for (int s = 0; s < p.nsplit; s++) M = fmaxf(M, part[(size_t)s * (p.rank + 2)]);
+  float L = 0.f;
+  for (int s = 0; s < p.nsplit; s++) {
+    const float ms = part[(size_t)s * (p.rank + 2)];
+    if (ms != -INFINITY) L = fmaf(part[(size_t)s * (p.rank + 2) + 1], expf(ms - M), L);
+  }
+  T *out = reinterpret_cast<T *>(p.lat) + (size_t)mh * p.rank;
+  for (int c = threadIdx.x; c < p.rank; c += blockDim.x) {
+    float a = 0.f;
+    for (int s = 0; s < p.nsplit; s++) {
+      const float ms = part[(size_t)s * (p.rank + 2)];
+      if (ms != -INFINITY) a = fmaf(part[(size_t)s * (p.rank + 2) + 2 + c], expf(ms - M), a);
+    }
+    out[c] = DT<T>::from_f(a / L);
+  }
+}
+
+// weights of the matrix-product form: one warp per (token, head) row of the block
+template <typename T>
+__global__ void __launch_bounds__(128) latent_softmax_kernel(const LatentSoftmax p) {
+  const long row = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= (long)p.n_tok * p.heads) return;
+  const int t = (int)(row / p.heads), n_keys = min(p.kp, p.pos_first + t + 1);
+  const float *s = p.scores + (size_t)row * p.kp;
+  T *w = reinterpret_cast<T *>(p.w) + (size_t)row * 2 * p.kp;
+  float mx = -INFINITY;
+  for (int j = lane; j < n_keys; j += 32) mx = fmaxf(mx, s[j]);
+  mx = warp_max(mx) * p.scale;
+  float l = 0.f;
+  for (int j = lane; j < n_keys; j += 32) l += expf(fmaf(s[j], p.scale, -mx));
+  l = warp_sum(l);
+  const float il = 1.0f / l;
+  for (int j = lane; j < p.kp; j += 32) {
+    const float pr = j < n_keys ? expf(fmaf(s[j], p.scale, -mx)) * il : 0.f;
+    const T hi = DT<T>::from_f(pr);
+    w[j] = hi;
+    w[p.kp + j] = DT<T>::from_f(pr - DT<T>::to_f(hi));
+  }
+}
+int latent_softmax(cudaStream_t st, int dtype, const LatentSoftmax &p, uint64_t *launches) {
+  const long warps = (long)p.n_tok * p.heads;
+  if (p.scale <= 0.f) return (int)cudaErrorInvalidValue;  // the row maximum is taken before scaling
+  MX_DISPATCH(dtype, (latent_softmax_kernel<T><<<(unsigned)((warps + 3) / 4), 128, 0, st>>>(p)));
+  MX_DONE(1);
+}
+
 int latent_attention(cudaStream_t st, int dtype, const LatentAttn &p, uint64_t *launches) {
   const int Dk = p.rank + p.rot;
   if (Dk > 32 * 24) return (int)cudaErrorInvalidValue;
+  if (p.part && p.nsplit > 1) {
+    const dim3 grid((unsigned)(p.B * p.S * p.heads), (unsigned)p.nsplit);
+    const size_t smem = (size_t)4 * p.rank * sizeof(float);
+    MX_DISPATCH(dtype, {
+      if (Dk <= 32 * 6) latent_attn_split_kernel<T, 6><<<grid, 128, smem, st>>>(p);
+      else if (Dk <= 32 * 12) latent_attn_split_kernel<T, 12><<<grid, 128, smem, st>>>(p);
+      else latent_attn_split_kernel<T, 24><<<grid, 128, smem, st>>>(p);
+      latent_attn_merge_kernel<T><<<grid.x, 128, 0, st>>>(p);
+    });
+    MX_DONE(2);
+  }
   const long warps = (long)p.B * p.S * p.heads;
   const unsigned grid = (unsigned)((warps + 3) / 4);
   MX_DISPATCH(dtype, {
@@ -432,26 +574,24 @@ __global__ void moe_count_kernel(const int *ids, int n, int experts, int *counts
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n && ids[i] < experts) atomicAdd(&counts[ids[i]], 1);
 }
-// one thread: tiles of every expert's group; counts[e] becomes the group's first sorted position (the scatter's cursor)
+// one thread: every expert's pairs start on a multiple of `tile` sorted rows; counts[e] becomes that start (the scatter's cursor)
 __global__ void moe_tiles_kernel(const MoePlan p) {
   if (threadIdx.x != 0 || blockIdx.x != 0) return;
-  int row = 0, nt = 0;
+  int nt = 0;
   for (int e = 0; e < p.experts; e++) {
     const int cnt = p.counts[e];
-    p.counts[e] = row;
-    for (int r = 0; r < cnt && nt < p.max_tiles; r += p.tile) {
-      p.tile_expert[nt] = e;
-      p.tile_row0[nt] = row + r;
-      p.tile_rows[nt] = min(p.tile, cnt - r);
-      nt++;
-    }
-    row += cnt;
+    p.counts[e] = nt * p.tile;
+    for (int r = 0; r < cnt && nt < p.max_tiles; r += p.tile) p.tile_expert[nt++] = e;
   }
-  *p.n_tiles = nt;
+  for (; nt < p.max_tiles; nt++) p.tile_expert[nt] = -1;
 }
-__global__ void moe_scatter_kernel(const int *ids, int n, int experts, int *cursor, int *perm) {
+__global__ void moe_scatter_kernel(const int *ids, int n, int experts, int *cursor, int *perm, int *pos_of) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < n && ids[i] < experts) perm[atomicAdd(&cursor[ids[i]], 1)] = i;
+  if (i < n && ids[i] < experts) {
+    const int pos = atomicAdd(&cursor[ids[i]], 1);
+    perm[pos] = i;
+    pos_of[i] = pos;
+  }
 }
 int moe_route(cudaStream_t st, int dtype, const MoePlan &p, uint64_t *launches) {
   if (p.experts + p.identity > 32 * MOE_MAX_SLOTS || p.top > 32 || p.top < 1 || p.top > p.experts + p.identity) return (int)cudaErrorInvalidValue;
@@ -459,18 +599,38 @@ int moe_route(cudaStream_t st, int dtype, const MoePlan &p, uint64_t *launches) 
   int n = 1;
   if (p.experts > 0) {
     cudaMemsetAsync(p.counts, 0, sizeof(int) * (p.experts + 1), st);
+    cudaMemsetAsync(p.perm, 0xff, sizeof(int) * (size_t)p.max_tiles * p.tile, st);
     const int ne = p.M * p.top;
     moe_count_kernel<<<(ne + 255) / 256, 256, 0, st>>>(p.ids, ne, p.experts, p.counts);
     moe_tiles_kernel<<<1, 32, 0, st>>>(p);
-    moe_scatter_kernel<<<(ne + 255) / 256, 256, 0, st>>>(p.ids, ne, p.experts, p.counts, p.perm);
+    moe_scatter_kernel<<<(ne + 255) / 256, 256, 0, st>>>(p.ids, ne, p.experts, p.counts, p.perm, p.pos_of);
     n += 3;
   }
   MX_DONE(n);
 }
 
+template <typename T>
+__global__ void __launch_bounds__(128) moe_gather_kernel(const T *__restrict__ h, const int *__restrict__ perm, T *__restrict__ sorted, int W, int top) {
+  const size_t r = blockIdx.x;
+  const int e = perm[r];
+  T *dst = sorted + r * W;
+  const T *src = e >= 0 ? h + (size_t)(e / top) * W : nullptr;
+  constexpr int VE = 16 / (int)sizeof(T);
+  if (W % VE == 0) {
+    for (int i = threadIdx.x; i < W / VE; i += blockDim.x)
+      reinterpret_cast<uint4 *>(dst)[i] = src ? reinterpret_cast<const uint4 *>(src)[i] : make_uint4(0, 0, 0, 0);
+    return;
+  }
+  for (int i = threadIdx.x; i < W; i += blockDim.x) dst[i] = src ? src[i] : DT<T>::from_f(0.f);
+}
+int moe_gather(cudaStream_t st, int dtype, const void *h, const int *perm, void *sorted, int rows, int W, int top, uint64_t *launches) {
+  MX_DISPATCH(dtype, (moe_gather_kernel<T><<<rows, 128, 0, st>>>(reinterpret_cast<const T *>(h), perm, reinterpret_cast<T *>(sorted), W, top)));
+  MX_DONE(1);
+}
+
 // ---------------------------------------------------------------------------------------------- experts
-// Tiles of up to `tile` (= 64) sorted rows that share an expert.  PHASE 0: act = f(Wg h) * (Wu h) into the sorted scratch;
-// PHASE 1: y[m * top + slot] = weight * (Wd act).
+// A block of `tile` (= 64) sorted rows shares an expert.  PHASE 0: act = f(Wg h) * (Wu h) into the sorted scratch;
+// PHASE 1: y[sorted row] = Wd act.
 constexpr int ME_BM = 64, ME_BN = 64, ME_BK = 16;
 __device__ __forceinline__ float act_f(float g, int kind) {
   if (kind) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * g * (1.0f + 0.044715f * g * g)));
@@ -478,33 +638,36 @@ __device__ __forceinline__ float act_f(float g, int kind) {
 }
 template <typename T, int PHASE>
 __global__ void __launch_bounds__(256) moe_expert_kernel(const MoeExperts p) {
-  const int tl = blockIdx.y;
-  if (tl >= *p.n_tiles) return;
+  const int tl = blockIdx.y, e = p.tile_expert[tl];
+  if (e < 0) return;
   __shared__ float As[ME_BK][ME_BM + 4];
   __shared__ float Ws[ME_BK][ME_BN + 4];
   __shared__ float Us[PHASE == 0 ? ME_BK : 1][ME_BN + 4];
   __shared__ int src[ME_BM];
-  const int e = p.tile_expert[tl], row0 = p.tile_row0[tl], rows = p.tile_rows[tl];
+  const int row0 = tl * ME_BM;
   const int K = PHASE == 0 ? p.W : p.ff, N = PHASE == 0 ? p.ff : p.W;
-  for (int r = threadIdx.x; r < ME_BM; r += 256) src[r] = r < rows ? p.perm[row0 + r] : -1;
+  for (int r = threadIdx.x; r < ME_BM; r += 256) src[r] = p.perm[row0 + r];
   __syncthreads();
   const T *A = PHASE == 0 ? reinterpret_cast<const T *>(p.h) : reinterpret_cast<const T *>(p.act);
-  const T *Wa = PHASE == 0 ? reinterpret_cast<const T *>(p.wg) + (size_t)e * p.ff * p.W : reinterpret_cast<const T *>(p.wd) + (size_t)e * p.W * p.ff;
-  const T *Wb = reinterpret_cast<const T *>(p.wu) + (size_t)e * p.ff * p.W;
+  const T *Wa = PHASE == 0 ? reinterpret_cast<const T *>(p.wgu) + (size_t)e * 2 * p.ff * p.W : reinterpret_cast<const T *>(p.wd) + (size_t)e * p.W * p.ff;
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4, n0 = blockIdx.x * ME_BN;
   float acc[4][4] = {}, acu[4][4] = {};
   for (int k0 = 0; k0 < K; k0 += ME_BK) {
     for (int i = threadIdx.x; i < ME_BM * ME_BK; i += 256) {
       const int r = i / ME_BK, c = i % ME_BK;
       float a = 0.f;
-      if (r < rows && k0 + c < K) {
+      if (src[r] >= 0 && k0 + c < K) {
         const size_t arow = PHASE == 0 ? (size_t)(src[r] / p.top) : (size_t)(row0 + r);
         a = DT<T>::to_f(A[arow * K + k0 + c]);
       }
       As[c][r] = a;
       const bool ok = n0 + r < N && k0 + c < K;
-      Ws[c][r] = ok ? DT<T>::to_f(Wa[(size_t)(n0 + r) * K + k0 + c]) : 0.f;
-      if (PHASE == 0) Us[c][r] = ok ? DT<T>::to_f(Wb[(size_t)(n0 + r) * K + k0 + c]) : 0.f;
+      if (PHASE == 0) {
+        Ws[c][r] = ok ? DT<T>::to_f(Wa[(size_t)(2 * (n0 + r)) * K + k0 + c]) : 0.f;
+        Us[c][r] = ok ? DT<T>::to_f(Wa[(size_t)(2 * (n0 + r) + 1) * K + k0 + c]) : 0.f;
+      } else {
+        Ws[c][r] = ok ? DT<T>::to_f(Wa[(size_t)(n0 + r) * K + k0 + c]) : 0.f;
+      }
     }
     __syncthreads();
 #pragma unroll
@@ -529,7 +692,7 @@ __global__ void __launch_bounds__(256) moe_expert_kernel(const MoeExperts p) {
 #pragma unroll
   for (int i = 0; i < 4; i++) {
     const int r = ty * 4 + i;
-    if (r >= rows) continue;
+    if (src[r] < 0) continue;
 #pragma unroll
     for (int j = 0; j < 4; j++) {
       const int n = n0 + tx * 4 + j;
@@ -538,7 +701,7 @@ __global__ void __launch_bounds__(256) moe_expert_kernel(const MoeExperts p) {
         const float g = rnd<T>(act_f(rnd<T>(acc[i][j]), p.act_kind));
         reinterpret_cast<T *>(p.act)[(size_t)(row0 + r) * p.ff + n] = DT<T>::from_f(g * rnd<T>(acu[i][j]));
       } else {
-        p.y[(size_t)src[r] * p.W + n] = p.wts[src[r]] * acc[i][j];
+        p.y[(size_t)(row0 + r) * p.W + n] = acc[i][j];
       }
     }
   }
@@ -559,8 +722,9 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const MoeCombine p) {
   for (int i = threadIdx.x; i < p.W; i += blockDim.x) {
     float s = 0.f;
     for (int k = 0; k < p.top; k++) {
-      const int e = p.ids[(size_t)m * p.top + k];
-      s += e < p.experts ? p.y[((size_t)m * p.top + k) * p.W + i] : p.wts[(size_t)m * p.top + k] * DT<T>::to_f(h[i]);
+      const size_t pr = (size_t)m * p.top + k;
+      const int e = p.ids[pr];
+      s = fmaf(p.wts[pr], e < p.experts ? p.y[(size_t)p.pos_of[pr] * p.W + i] : DT<T>::to_f(h[i]), s);
     }
     p.x_out[(size_t)m * p.W + i] = p.x[(size_t)m * p.W + i] + s;
   }

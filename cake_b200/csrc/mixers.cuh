@@ -25,6 +25,8 @@ struct LatentPrep {
   const float *cos_t, *sin_t;  // [positions, rope_dims / 2]
   int rope_dims;         // <= rot: leading entries of the rotated part that are rotated (pairs i, i + rope_dims / 2)
   void *cache;           // [B, cap, rank + rot] D: the normed latent and the rotated shared key part
+  void *cache_t;         // nullptr, or [B, rank, cap_t] D: the latent once more with the positions innermost (the second
+  int cap_t;             // operand of the weights-times-latent product when it runs as a plain matrix product)
   void *qa;              // [M, heads, rank + rot] D: the rotated query part lands in columns rank..; columns 0..rank-1 are
                          // filled afterwards by the product of the unrotated query with the key expansion
   int B, S, heads, dim, rot, rank, cap, pos0;
@@ -39,8 +41,23 @@ struct LatentAttn {
   void *lat;             // [M, heads, rank] D
   int B, S, heads, rank, rot, cap, pos0;
   float scale;
+  // steps of a few rows: the keys of a (row, head) are split over nsplit CTAs whose partial (max, sum, weighted latent)
+  // land in part [M * heads, nsplit, rank + 2] fp32 and are merged by a second kernel; nsplit <= 1: one warp per (row, head)
+  float *part = nullptr;
+  int nsplit = 0;
 };
 int latent_attention(cudaStream_t, int dtype, const LatentAttn &, uint64_t *launches);
+
+// The same attention as matrix products for long portions in 16-bit D: scores [rows, kp] fp32 (rows = (t, head) pairs of `n_tok`
+// tokens starting at step offset t0, kp keys padded to the product's tile) -> masked, scaled softmax -> the weights as
+// w_hi + w_lo in D, [rows, 2 * kp]: hi in columns [0, kp), lo in [kp, 2 kp), zeros where row t sees no key.
+struct LatentSoftmax {
+  const float *scores;
+  void *w;
+  int n_tok, heads, kp, pos_first;   // pos_first: absolute position of the block's first token (it sees keys 0..pos_first)
+  float scale;
+};
+int latent_softmax(cudaStream_t, int dtype, const LatentSoftmax &, uint64_t *launches);
 
 // ---- batched small products: C[z][m, n] = sum_k A[z][m, k] * W[z][n, k]  (w_kn: W[z][k, n]) -------------------------------
 struct HeadGemm {
@@ -113,36 +130,39 @@ struct MoePlan {
   int *ids;              // [M, top]
   float *wts;            // [M, top]
   float *sgate;          // [M]
-  // grouping of the (token, slot) pairs by expert in tiles of `tile` rows
+  // grouping of the (token, slot) pairs by expert: every expert's pairs start on a multiple of `tile` sorted rows
   int tile;
   int *counts;           // [experts + 1] scratch
-  int *perm;             // [M * top]: sorted position -> m * top + slot
-  int *tile_expert, *tile_row0, *tile_rows;  // [max_tiles]
-  int *n_tiles;          // [1]
+  int *perm;             // [max_tiles * tile]: sorted row -> m * top + slot, or -1 (padding)
+  int *pos_of;           // [M * top]: m * top + slot -> sorted row (pairs of identity experts: untouched)
+  int *tile_expert;      // [max_tiles]: the expert of a block of `tile` sorted rows, or -1 (unused block)
   int max_tiles;
 };
 int moe_route(cudaStream_t, int dtype, const MoePlan &, uint64_t *launches);
 
+// sorted[r] = h[perm[r] / top] (zeros for padding rows): the operand of a grouped product on the tensor cores
+int moe_gather(cudaStream_t, int dtype, const void *h, const int *perm, void *sorted, int rows, int W, int top, uint64_t *launches);
+
+// CUDA-core experts for every shape and D = float: act = f(Wg h) * (Wu h), then y[sorted row] = Wd act
 struct MoeExperts {
   const void *h;         // [M, W] D
-  const void *wg, *wu;   // [experts, ff, W] D
+  const void *wgu;       // [experts, 2 * ff, W] D: row 2i = gate_i, row 2i + 1 = up_i
   const void *wd;        // [experts, W, ff] D
-  void *act;             // [M * top, ff] D scratch (sorted order)
-  float *y;              // [M * top, W] fp32: weighted expert outputs at row m * top + slot
+  void *act;             // [max_tiles * tile, ff] D scratch
+  float *y;              // [max_tiles * tile, W] fp32: expert outputs in sorted order, not yet weighted
   int M, W, ff, top, act_kind;
-  const int *perm, *tile_expert, *tile_row0, *tile_rows, *n_tiles;
-  const float *wts;
+  const int *perm, *tile_expert;
   int tile, max_tiles;
 };
 int moe_experts(cudaStream_t, int dtype, const MoeExperts &, uint64_t *launches);
 
-// x_out[m] = x[m] + sum over slots (expert: y[m * top + slot]; identity: wts * h[m]), slots in order
+// x_out[m] = x[m] + sum over slots of wts * (expert: y[pos_of[m * top + slot]]; identity: h[m]), slots in order
 struct MoeCombine {
   const float *x;
   float *x_out;
   const void *h;         // [M, W] D
   const float *y, *wts;
-  const int *ids;
+  const int *ids, *pos_of;
   int M, W, top, experts;
 };
 int moe_combine(cudaStream_t, int dtype, const MoeCombine &, uint64_t *launches);

@@ -357,6 +357,30 @@ def test_other_sizes_bf16_and_tensor_core_shapes():
 
 
 @pytest.mark.gpu
+def test_long_portions_on_the_tensor_cores():
+    """Sizes at which long portions in bf16 take the matrix-product form of the latent attention (several blocks of rows, with
+    and without keys from earlier portions) and the grouped expert products, against the plain model and against the same
+    positions decoded through the per-row kernels."""
+    layers = [latent(heads=8, dim=32, rot_dim=64, vdim=32, kv_rank=128, scale=0.6, moe=moe(experts=6, identity=1, top=2, ff=64, shared_ff=128)),
+              retention(heads=2, dim=32, vdim=64, rot_dims=32, decay=[0.97, 0.995], moe=None)]
+    cfg = make_config(layers, width=128, vocab=96, max_seq=1024)
+    sd = make_mixer_checkpoint(cfg, "bf16", seed=71)
+    toks = tokens(700, cfg.vocab_size, seed=13)
+    want = plain(cfg, sd, toks)
+    r = Runner(cfg, sd, "bf16")
+    try:
+        whole = r.run("w", toks)
+        close(whole, want, "bf16", "whole")
+        cut = r.run("c", toks, cuts=[300, 390, 2, 1])
+        close(cut, want, "bf16", "portions")
+        small = r.run("s", toks, cuts=[100])       # every portion below the matrix-product threshold
+        close(small, want, "bf16", "short portions")
+        assert np.quantile(errors(whole, small), 0.95) < TOL["bf16"]
+    finally:
+        r.close()
+
+
+@pytest.mark.gpu
 def test_greedy_generation_through_master():
     from cake_b200.model import Context, Master, TextModelBase
     cfg = full_config()
