@@ -207,7 +207,7 @@ struct cake_b200_block {
   cake_b200_mixer_spec ms{};
   void *m_dkv_norm = nullptr, *m_uk = nullptr, *m_uv = nullptr;
   void *m_conv = nullptr, *m_conv_b = nullptr, *m_dt_bias = nullptr, *m_a_log = nullptr, *m_d = nullptr, *m_norm = nullptr;
-  void *m_router = nullptr, *m_corr = nullptr, *m_eg = nullptr, *m_ed = nullptr, *m_sg = nullptr;
+  void *m_router = nullptr, *m_corr = nullptr, *m_eg = nullptr, *m_ed = nullptr;
   float *m_cos = nullptr, *m_sin = nullptr, *m_decay = nullptr;
   int m_rope_rows = 0;
   bool variant() const { return !ln1 || !ln2 || pan || pfn || window >= 0 || !use_rope || ctx->cfg.pre_reshape_qk_norm; }
@@ -735,7 +735,7 @@ extern "C" void cake_b200_block_free(cake_b200_block *b) {
   cudaSetDevice(b->device);
   void *bufs[] = {b->wqkv, b->wo, b->wgu, b->wd, b->ln1, b->ln2, b->bqkv, b->qn, b->kn, b->pan, b->pfn,
                   b->w_in, b->w_out, b->g, b->shift, b->r1, b->r2, b->m_dkv_norm, b->m_uk, b->m_uv, b->m_conv, b->m_conv_b, b->m_dt_bias,
-                  b->m_a_log, b->m_d, b->m_norm, b->m_router, b->m_corr, b->m_eg, b->m_ed, b->m_sg, b->m_cos, b->m_sin, b->m_decay};
+                  b->m_a_log, b->m_d, b->m_norm, b->m_router, b->m_corr, b->m_eg, b->m_ed, b->m_cos, b->m_sin, b->m_decay};
   for (void *p : bufs)
     if (p) cudaFree(p);  // cudaFree synchronises with outstanding work
   (void)cudaGetLastError();
@@ -1684,7 +1684,14 @@ extern "C" int cake_b200_block_load_mixer(cake_b200_ctx *c, int layer_idx, const
     if (has_ff) {
       const size_t E = mo.experts, Et = E + mo.identity, I = mo.ff, Is = mo.shared_ff;
       RC(upload(c, &b->ln2, t->norm2, H * es));
-      RC(upload(c, &b->m_router, t->router, Et * H * es));
+      // router rows, then the shared expert's gate vector as one more row, zero rows up to the tensor-core tile: one product
+      // gives every logit of a token
+      const size_t NP = (size_t)round_up((int)Et + 1, TC_BN);
+      CU(cudaMalloc(&b->m_router, NP * H * es + 16));
+      CU(cudaMemsetAsync(b->m_router, 0, NP * H * es, 0));
+      CU(cudaStreamSynchronize(0));
+      RC(pipe_copy(c, b->m_router, Et * H * es, t->router, Et * H * es, Et * H * es, 1));
+      if (Is) RC(pipe_copy(c, (char *)b->m_router + Et * H * es, H * es, t->s_sg, H * es, H * es, 1));
       RC(upload(c, &b->m_corr, t->correction, Et * es));
       if (E) {
         // all experts stacked: gate / up row-interleaved per expert (as the dense blocks lay theirs out) and the down matrices,
@@ -1704,7 +1711,6 @@ extern "C" int cake_b200_block_load_mixer(cake_b200_ctx *c, int layer_idx, const
         RC(pipe_copy(c, b->wgu, 2 * H * es, t->s_gate, H * es, H * es, Is));
         RC(pipe_copy(c, (char *)b->wgu + H * es, 2 * H * es, t->s_up, H * es, H * es, Is));
         RC(upload(c, &b->wd, t->s_down, H * Is * es));
-        RC(upload(c, &b->m_sg, t->s_sg, H * es));
       }
     }
     return pipe_mark(c);
@@ -1756,7 +1762,7 @@ static int cache_ensure_mixer(cake_b200_cache *k, int layer, const cake_b200_blo
 // scratch of one block for M rows, carved from the ctx arena (base == nullptr: sizes only)
 struct MixerScratch {
   void *h, *proj, *qa, *lat, *att, *conv, *act, *sact, *sorted, *pw;
-  float *o32, *wts, *sgate, *y, *part, *scores;
+  float *o32, *wts, *sgate, *y, *part, *scores, *logits;
   int nsplit, lat_tok;
   int *ids, *counts, *perm, *pos_of, *tile_expert;
   int max_tiles, tile;
@@ -1803,6 +1809,7 @@ static MixerScratch mixer_scratch(const cake_b200_ctx *c, const cake_b200_block 
     s.tile = moe_on_tc(c, b) ? TC_BM : 64;
     s.max_tiles = (int)((nt + s.tile - 1) / s.tile + std::min<size_t>(mo.experts, nt));
     const size_t rows = (size_t)s.max_tiles * s.tile;
+    s.logits = (float *)take(M * (size_t)round_up(mo.experts + mo.identity + 1, TC_BN) * sizeof(float));
     s.ids = (int *)take(nt * sizeof(int));
     s.wts = (float *)take(nt * sizeof(float));
     s.sgate = (float *)take(M * sizeof(float));
@@ -1924,7 +1931,11 @@ static int enqueue_mixer_layers(cake_b200_ctx *c, cake_b200_block *const *blocks
       if (mo.experts + mo.identity > 0) {
         RC(launch_pdl(c, norm_shift_rows_kernel<T>, dim3(M), dim3(256), 0, cur, (const int *)nullptr, 1, 0, (const T *)b->ln2, 1, (const T *)nullptr,
                       (const float *)nullptr, (float *)nullptr, (T *)w.h, (T *)nullptr, S, H, c->cfg.rms_eps, pos0));
-        mx::MoePlan mp{w.h, b->m_router, b->m_corr, mo.shared_ff ? b->m_sg : nullptr, M, H, mo.experts, mo.identity, mo.top, mo.scale, w.ids, w.wts,
+        const int NP = round_up(mo.experts + mo.identity + 1, TC_BN);
+        RowsGemm gr{w.h, b->m_router, nullptr, w.logits, M, NP, H, H, NP, 0, 0.f};
+        if (listed_tc<T>(c, M, NP, H)) RC((listed_gemm_tc<T, TCE_SOFTCAP_F32>(c, w.h, b->m_router, nullptr, w.logits, M, NP, H, 0, 0)));
+        else RC((gemm_rows_T<T, RE_SOFTCAP_F32>(c, gr)));
+        mx::MoePlan mp{w.logits, NP, b->m_corr, mo.shared_ff ? 1 : 0, M, H, mo.experts, mo.identity, mo.top, mo.scale, w.ids, w.wts,
                        w.sgate, w.tile, w.counts, w.perm, w.pos_of, w.tile_expert, w.max_tiles};
         MX(mx::moe_route(st, dt, mp, lc));
         if (mo.experts && w.sorted) {  // grouped products: sorted rows of h -> act(gate) * up -> down, expert e at row e * N of the stacked weights

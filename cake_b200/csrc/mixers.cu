@@ -409,8 +409,124 @@ __global__ void recurrence_kernel(const Recurrence p) {
   }
   for (int i = threadIdx.x; i < dk * dv; i += blockDim.x) gstate[i] = St[i];
 }
+// The same recurrence for key sizes of 8 R and value sizes that are multiples of 32.  The columns of the state are
+// independent, so a CTA owns 32 of them for one (head, batch row): warp s keeps rows s R .. s R + R - 1 of its lanes' columns in
+// registers.  Tokens come in chunks of 16: their q, k (rotated, scaled) and v are staged in shared memory once, the 16 updates
+// run without a barrier, and the eight warps' partial outputs are added up once per chunk.
+constexpr int RC_TT = 16, RC_CB = 32, RC_RS = 8;
+template <typename T, int R>
+__global__ void __launch_bounds__(256) recurrence_cols_kernel(const Recurrence p) {
+  extern __shared__ float sm[];
+  constexpr int dk = R * RC_RS;
+  float *qs = sm, *ks = qs + RC_TT * dk, *vs = ks + RC_TT * dk, *as = vs + RC_TT * RC_CB, *bs = as + RC_TT, *part = bs + RC_TT;
+  const int ncb = p.dv / RC_CB, h = blockIdx.x / ncb, cb = blockIdx.x % ncb, b = blockIdx.y;
+  const int lane = threadIdx.x & 31, s = threadIdx.x >> 5;
+  float St[R];
+  float *gstate = p.state + (((size_t)b * p.heads + h) * dk + (size_t)s * R) * p.dv + cb * RC_CB + lane;
+#pragma unroll
+  for (int r = 0; r < R; r++) St[r] = p.pos0 > 0 ? gstate[(size_t)r * p.dv] : 0.f;
+  const int gcol = (h / p.group_div) * dk, half = p.rope_dims >> 1;
+  const T *dtb = reinterpret_cast<const T *>(p.dt_bias), *alog = reinterpret_cast<const T *>(p.a_log), *skp = reinterpret_cast<const T *>(p.skip);
+  const float nexpA = p.dt ? -expf(DT<T>::to_f(alog[h])) : 0.f, bias = p.dt ? DT<T>::to_f(dtb[h]) : 0.f;
+  const float skip = skp ? DT<T>::to_f(skp[h]) : 0.f;
+  for (int t0 = 0; t0 < p.S; t0 += RC_TT) {
+    const int nt = min(RC_TT, p.S - t0);
+    const size_t m0 = (size_t)b * p.S + t0;
+    __syncthreads();  // the previous chunk's outputs have been added up
+    if ((int)threadIdx.x < nt) {
+      float a = p.decay ? p.decay[h] : 1.f, bsc = p.kscale;
+      if (p.dt) {
+        const float d = softplus_f(DT<T>::to_f(reinterpret_cast<const T *>(p.dt)[(m0 + threadIdx.x) * p.lddt + h]) + bias);
+        a = expf(nexpA * d);
+        bsc = d;
+      }
+      as[threadIdx.x] = a;
+      bs[threadIdx.x] = bsc;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < nt * dk; idx += 256) {
+      const int tt = idx / dk, i = idx % dk;
+      const T *qr = reinterpret_cast<const T *>(p.q) + (m0 + tt) * p.ldq + gcol;
+      const T *kr = reinterpret_cast<const T *>(p.k) + (m0 + tt) * p.ldk + gcol;
+      if (p.cos_t) {
+        const float *cs = p.cos_t + (size_t)(p.pos0 + t0 + tt) * half, *sn = p.sin_t + (size_t)(p.pos0 + t0 + tt) * half;
+        qs[idx] = rotated<T>(qr, i, p.rope_dims, cs, sn);
+        ks[idx] = rotated<T>(kr, i, p.rope_dims, cs, sn) * bs[tt];
+      } else {
+        qs[idx] = DT<T>::to_f(qr[i]);
+        ks[idx] = DT<T>::to_f(kr[i]) * bs[tt];
+      }
+    }
+    for (int idx = threadIdx.x; idx < nt * RC_CB; idx += 256) {
+      const int tt = idx / RC_CB, j = idx % RC_CB;
+      vs[idx] = DT<T>::to_f(reinterpret_cast<const T *>(p.v)[(m0 + tt) * p.ldv + (size_t)h * p.dv + cb * RC_CB + j]);
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nt; tt++) {
+      const float a = as[tt], v = vs[tt * RC_CB + lane];
+      const float *kq = ks + tt * dk + s * R, *qq = qs + tt * dk + s * R;
+      float acc = 0.f;
+      if (R % 4 == 0) {
+#pragma unroll
+        for (int r = 0; r < R; r += 4) {
+          const float4 k4 = *reinterpret_cast<const float4 *>(kq + r), q4 = *reinterpret_cast<const float4 *>(qq + r);
+          St[r] = fmaf(a, St[r], k4.x * v); acc = fmaf(St[r], q4.x, acc);
+          St[r + 1] = fmaf(a, St[r + 1], k4.y * v); acc = fmaf(St[r + 1], q4.y, acc);
+          St[r + 2] = fmaf(a, St[r + 2], k4.z * v); acc = fmaf(St[r + 2], q4.z, acc);
+          St[r + 3] = fmaf(a, St[r + 3], k4.w * v); acc = fmaf(St[r + 3], q4.w, acc);
+        }
+      } else {
+#pragma unroll
+        for (int r = 0; r < R; r += 2) {
+          const float2 k2 = *reinterpret_cast<const float2 *>(kq + r), q2 = *reinterpret_cast<const float2 *>(qq + r);
+          St[r] = fmaf(a, St[r], k2.x * v); acc = fmaf(St[r], q2.x, acc);
+          St[r + 1] = fmaf(a, St[r + 1], k2.y * v); acc = fmaf(St[r + 1], q2.y, acc);
+        }
+      }
+      part[(s * RC_TT + tt) * RC_CB + lane] = acc;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < nt * RC_CB; idx += 256) {
+      const int tt = idx / RC_CB, j = idx % RC_CB;
+      float o = 0.f;
+#pragma unroll
+      for (int w = 0; w < RC_RS; w++) o += part[(w * RC_TT + tt) * RC_CB + j];
+      p.o[(m0 + tt) * ((size_t)p.heads * p.dv) + (size_t)h * p.dv + cb * RC_CB + j] = fmaf(skip, vs[idx], o);
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < R; r++) gstate[(size_t)r * p.dv] = St[r];
+}
+template <typename T, int R> static cudaError_t launch_recurrence_cols(cudaStream_t st, const Recurrence &p) {
+  constexpr int dk = R * RC_RS;
+  const size_t smem = (size_t)(2 * RC_TT * dk + RC_TT * RC_CB + 2 * RC_TT + RC_RS * RC_TT * RC_CB) * sizeof(float);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(recurrence_cols_kernel<T, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+  }
+  recurrence_cols_kernel<T, R><<<dim3(p.heads * (p.dv / RC_CB), p.B), 256, smem, st>>>(p);
+  return cudaSuccess;
+}
+
 int recurrence(cudaStream_t st, int dtype, const Recurrence &p, uint64_t *launches) {
   if (p.dv > 1024 || p.dk < 1) return (int)cudaErrorInvalidValue;
+  if (p.dk % RC_RS == 0 && p.dv % RC_CB == 0) {
+    cudaError_t e = cudaErrorNotSupported;
+    MX_DISPATCH(dtype, {
+      switch (p.dk / RC_RS) {
+        case 4: e = launch_recurrence_cols<T, 4>(st, p); break;
+        case 6: e = launch_recurrence_cols<T, 6>(st, p); break;
+        case 8: e = launch_recurrence_cols<T, 8>(st, p); break;
+        case 12: e = launch_recurrence_cols<T, 12>(st, p); break;
+        case 16: e = launch_recurrence_cols<T, 16>(st, p); break;
+        case 24: e = launch_recurrence_cols<T, 24>(st, p); break;
+        case 32: e = launch_recurrence_cols<T, 32>(st, p); break;
+        default: break;
+      }
+    });
+    if (e == cudaSuccess) MX_DONE(1);
+    if (e != cudaErrorNotSupported) return (int)e;
+  }
   const int threads = p.dv <= 256 ? 256 : (p.dv + 31) / 32 * 32;
   const int RS = threads / p.dv > 0 ? threads / p.dv : 1;
   const size_t smem = ((size_t)p.dk * p.dv + 2 * p.dk + p.dv + (size_t)RS * p.dv) * sizeof(float);
@@ -507,20 +623,11 @@ __global__ void __launch_bounds__(128) moe_router_kernel(const MoePlan p) {
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (warp >= p.M) return;
   const int m = warp, E = p.experts + p.identity;
-  const T *h = reinterpret_cast<const T *>(p.h) + (size_t)m * p.W;
-  const T *Wr = reinterpret_cast<const T *>(p.router), *corr = reinterpret_cast<const T *>(p.correction);
+  const float *lg = p.logits + (size_t)m * p.ld;
+  const T *corr = reinterpret_cast<const T *>(p.correction);
   float z[MOE_MAX_SLOTS];
 #pragma unroll
-  for (int sI = 0; sI < MOE_MAX_SLOTS; sI++) z[sI] = -INFINITY;
-  for (int e = 0; e < E; e++) {
-    const T *wr = Wr + (size_t)e * p.W;
-    float d = 0.f;
-    for (int i = lane; i < p.W; i += 32) d = fmaf(DT<T>::to_f(h[i]), DT<T>::to_f(wr[i]), d);
-    d = warp_sum(d);
-#pragma unroll
-    for (int sI = 0; sI < MOE_MAX_SLOTS; sI++)
-      if (e == lane + 32 * sI) z[sI] = d;
-  }
+  for (int sI = 0; sI < MOE_MAX_SLOTS; sI++) z[sI] = lane + 32 * sI < E ? lg[lane + 32 * sI] : -INFINITY;
   float mx = -INFINITY;
 #pragma unroll
   for (int sI = 0; sI < MOE_MAX_SLOTS; sI++) mx = fmaxf(mx, z[sI]);
@@ -562,13 +669,7 @@ __global__ void __launch_bounds__(128) moe_router_kernel(const MoePlan p) {
     p.ids[(size_t)m * p.top + lane] = mine_id;
     p.wts[(size_t)m * p.top + lane] = mine / (wsum + 1e-20f) * p.scale;
   }
-  if (p.shared_gate) {
-    const T *sg = reinterpret_cast<const T *>(p.shared_gate);
-    float d = 0.f;
-    for (int i = lane; i < p.W; i += 32) d = fmaf(DT<T>::to_f(h[i]), DT<T>::to_f(sg[i]), d);
-    d = warp_sum(d);
-    if (lane == 0) p.sgate[m] = 1.0f / (1.0f + expf(-d));
-  }
+  if (p.has_shared_gate && lane == 0) p.sgate[m] = 1.0f / (1.0f + expf(-lg[E]));
 }
 __global__ void moe_count_kernel(const int *ids, int n, int experts, int *counts) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;

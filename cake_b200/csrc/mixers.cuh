@@ -118,13 +118,13 @@ struct GateNorm {
 int gate_norm(cudaStream_t, int dtype, const GateNorm &, uint64_t *launches);
 
 // ---- routed feed-forward ---------------------------------------------------------------------------------------------
-// Router: z = Wr h (fp32), s = softmax(z); the `top` largest s + correction are chosen; weights = s / (sum of chosen + 1e-20)
+// Router: z = Wr h (fp32, a matrix product done by the caller), s = softmax(z); the `top` largest s + correction are chosen; weights = s / (sum of chosen + 1e-20)
 // * scale.  Experts [0, experts) are gated feed-forwards, [experts, experts + identity) return their input.
 struct MoePlan {
-  const void *h;         // [M, W] D
-  const void *router;    // [experts + identity, W] D
+  const float *logits;   // [M, ld] fp32: router logits in columns [0, experts + identity); with has_shared_gate the logit of the
+  int ld;                // shared expert's gate in the next column (sigmoid of it -> sgate[m])
   const void *correction;// [experts + identity] D
-  const void *shared_gate; // [W] D or nullptr: sigmoid(shared_gate . h) -> sgate[m]
+  int has_shared_gate;
   int M, W, experts, identity, top;
   float scale;
   int *ids;              // [M, top]
