@@ -205,7 +205,7 @@ struct cake_b200_block {
   // routed feed-forward (w_in: the fused input projection, wo: the mixer's output projection, wgu / wd: the shared expert)
   bool mixer = false;
   cake_b200_mixer_spec ms{};
-  void *m_dkv_norm = nullptr, *m_uk = nullptr, *m_uv = nullptr;
+  void *m_dkv_norm = nullptr, *m_uk = nullptr, *m_uv = nullptr, *m_ukt = nullptr;  // m_ukt: uk per head as [kv_rank, dim]
   void *m_conv = nullptr, *m_conv_b = nullptr, *m_dt_bias = nullptr, *m_a_log = nullptr, *m_d = nullptr, *m_norm = nullptr;
   void *m_router = nullptr, *m_corr = nullptr, *m_eg = nullptr, *m_ed = nullptr;
   float *m_cos = nullptr, *m_sin = nullptr, *m_decay = nullptr;
@@ -734,7 +734,7 @@ extern "C" void cake_b200_block_free(cake_b200_block *b) {
   if (!b) return;
   cudaSetDevice(b->device);
   void *bufs[] = {b->wqkv, b->wo, b->wgu, b->wd, b->ln1, b->ln2, b->bqkv, b->qn, b->kn, b->pan, b->pfn,
-                  b->w_in, b->w_out, b->g, b->shift, b->r1, b->r2, b->m_dkv_norm, b->m_uk, b->m_uv, b->m_conv, b->m_conv_b, b->m_dt_bias,
+                  b->w_in, b->w_out, b->g, b->shift, b->r1, b->r2, b->m_dkv_norm, b->m_uk, b->m_uv, b->m_ukt, b->m_conv, b->m_conv_b, b->m_dt_bias,
                   b->m_a_log, b->m_d, b->m_norm, b->m_router, b->m_corr, b->m_eg, b->m_ed, b->m_cos, b->m_sin, b->m_decay};
   for (void *p : bufs)
     if (p) cudaFree(p);  // cudaFree synchronises with outstanding work
@@ -1163,6 +1163,7 @@ struct TcExtra {  // optional modes of the tensor-core GEMM (TcParams in gemm_tc
   const float *row_scale = nullptr;
   int b_kwrap = 0, w_cols = 0, w_ld = 0;  // W's k coordinate wraps at b_kwrap; its visible columns / row stride when not K
   int w_rows = 0;                         // W's visible rows when fewer than N (the rest reads as zeros)
+  int a_ld = 0;                           // A's row stride in elements when it is a column range of a wider buffer
 };
 template <typename T, int EPI>
 static int gemm_tc_T(cake_b200_ctx *c, const void *A, const void *W, const void *bias, const void *res, void *C, int M, int N, int K,
@@ -1176,7 +1177,7 @@ static int gemm_tc_T(cake_b200_ctx *c, const void *A, const void *W, const void 
   static const int no_mc = []() { const char *e = getenv("CAKE_B200_TC_MC"); return (e && e[0] == '0') ? 1 : 0; }();
   const bool mc = big && !no_mc && M % 256 == 0 && (tiles_m / 2) * (N / 256) >= c->sm_count / 2 && !x.tile_group && !x.b_kwrap;
   CUtensorMap ma, mb;
-  RC(make_tmap(&ma, A, (uint64_t)M, (uint64_t)K, c->cfg.dtype, TC_BM));
+  RC(make_tmap(&ma, A, (uint64_t)M, (uint64_t)K, c->cfg.dtype, TC_BM, (uint64_t)x.a_ld));
   RC(make_tmap(&mb, W, x.w_rows ? (uint64_t)x.w_rows : (uint64_t)N * x.n_groups, (uint64_t)(x.w_cols ? x.w_cols : K), c->cfg.dtype,
                mc ? 128u : (uint32_t)bn, (uint64_t)x.w_ld ? (uint64_t)x.w_ld : (uint64_t)K));
   TcParams p{bias, res, C, M, N, K, act >= 0 ? act : (c->cfg.use_gelu_mlp ? 1 : 0), ldc, cap, x.tile_group, x.row_scale, x.b_kwrap};
@@ -1578,6 +1579,18 @@ static int enqueue_listed_layers(cake_b200_ctx *c, cake_b200_block *const *block
     if (e_ != 0) return fail(CAKE_B200_ECUDA, "%s:%d %s -> %s", __FILE__, __LINE__, #call, cudaGetErrorString((cudaError_t)e_)); \
   } while (0)
 
+// Long portions of a latent-attention layer in 16-bit D run as matrix products on the tensor cores when the tiles cover the
+// shapes: scores = qa . cache^T (K = kv_rank + rot_dim), weighted latent = weights . latent (N = kv_rank).
+static bool latent_on_tc(const cake_b200_ctx *c, const cake_b200_block *b) {
+  static const bool no_tc = []() { const char *e = getenv("CAKE_B200_NO_TC"); return e && e[0] == '1'; }();
+  const cake_b200_mixer_spec &sp = b->ms;
+  return !no_tc && c->cfg.dtype != CAKE_B200_F32 && sp.kind == CAKE_B200_MIX_LATENT && (sp.kv_rank + sp.rot_dim) % TC_BK == 0 && sp.kv_rank % TC_BN == 0;
+}
+static int latent_cap_t(int cap) { return (cap + 63) / 64 * 64; }
+constexpr int LATENT_TC_ROWS = 4096;     // (token, head) rows per block of the matrix-product form
+constexpr int LATENT_TC_MIN_ROWS = 1024; // shorter steps take the per-row kernels
+constexpr int LATENT_SPLIT_MAX = 32;
+
 // cos / sin of position * frequency for `rows` positions, in double precision, with the optional frequency blend
 static void mixer_rope_tables(const cake_b200_rotary_spec &r, int rows, std::vector<float> &cs, std::vector<float> &sn) {
   const int half = r.dims / 2;
@@ -1662,6 +1675,12 @@ extern "C" int cake_b200_block_load_mixer(cake_b200_ctx *c, int layer_idx, const
       RC(upload(c, &b->m_dkv_norm, t->dkv_norm, (size_t)sp->kv_rank * es));
       RC(upload(c, &b->m_uk, t->uk, (size_t)sp->heads * sp->dim * sp->kv_rank * es));
       RC(upload(c, &b->m_uv, t->uv, inner * sp->kv_rank * es));
+      if (latent_on_tc(c, b)) {  // the key expansion with kv_rank outermost: the second operand of a plain product per head
+        CU(cudaMalloc(&b->m_ukt, (size_t)sp->heads * sp->dim * sp->kv_rank * es + 16));
+        RC(pipe_mark(c));
+        RC(wait_loads(c));
+        MX(mx::transpose_batched(c->stream, c->cfg.dtype, b->m_uk, b->m_ukt, sp->heads, sp->dim, sp->kv_rank, &c->launches));
+      }
     } else if (sp->kind == CAKE_B200_MIX_RETENTION) {
       RC(upload(c, (void **)&b->m_decay, sp->decay, sp->heads * sizeof(float)));
     } else {
@@ -1722,18 +1741,6 @@ extern "C" int cake_b200_block_load_mixer(cake_b200_ctx *c, int layer_idx, const
   *out = b;
   return CAKE_B200_OK;
 }
-
-// Long portions of a latent-attention layer in 16-bit D run as matrix products on the tensor cores when the tiles cover the
-// shapes: scores = qa . cache^T (K = kv_rank + rot_dim), weighted latent = weights . latent (N = kv_rank).
-static bool latent_on_tc(const cake_b200_ctx *c, const cake_b200_block *b) {
-  static const bool no_tc = []() { const char *e = getenv("CAKE_B200_NO_TC"); return e && e[0] == '1'; }();
-  const cake_b200_mixer_spec &sp = b->ms;
-  return !no_tc && c->cfg.dtype != CAKE_B200_F32 && sp.kind == CAKE_B200_MIX_LATENT && (sp.kv_rank + sp.rot_dim) % TC_BK == 0 && sp.kv_rank % TC_BN == 0;
-}
-static int latent_cap_t(int cap) { return (cap + 63) / 64 * 64; }
-constexpr int LATENT_TC_ROWS = 4096;     // (token, head) rows per block of the matrix-product form
-constexpr int LATENT_TC_MIN_ROWS = 1024; // shorter steps take the per-row kernels
-constexpr int LATENT_SPLIT_MAX = 32;
 
 static int cache_ensure_mixer(cake_b200_cache *k, int layer, const cake_b200_block *b) {
   if (layer < 0 || layer >= (int)k->k.size()) return fail(CAKE_B200_EINVAL, "block_idx %d out of range", layer);
@@ -1870,8 +1877,16 @@ static int enqueue_mixer_layers(cake_b200_ctx *c, cake_b200_block *const *blocks
                           B, S, sp.heads, sp.dim, sp.rot_dim, sp.kv_rank, kc->cap, pos0, c->cfg.rms_eps};
         MX(mx::latent_prep(st, dt, lp, lc));
         // the unrotated query through the key expansion: qa[m, h, :rank] = q[m, h, :dim] . uk[h]   (uk[h]: [dim, rank])
+        // long steps in 16-bit D: one tensor-core product per head on column ranges of the step's buffers
+        const bool heads_tc = b->m_ukt && M >= 512 && sp.dim % TC_BK == 0 && sp.vdim % TC_BN == 0 && qw % 8 == 0;
         mx::HeadGemm ga{w.proj, b->m_uk, w.qa, M, sp.kv_rank, sp.dim, sp.heads, qw, (long)sp.dim * sp.kv_rank, Dk, b->n_in_pad, sp.kv_rank, sp.heads * Dk, 1};
-        MX(mx::head_gemm(st, dt, ga, lc));
+        if (heads_tc) {
+          TcExtra xa;
+          xa.a_ld = b->n_in_pad;
+          for (int hh = 0; hh < sp.heads; hh++)
+            RC((listed_gemm_tc<T, TCE_PLAIN>(c, (const T *)w.proj + (size_t)hh * qw, (const T *)b->m_ukt + (size_t)hh * sp.kv_rank * sp.dim, nullptr,
+                                             (T *)w.qa + (size_t)hh * Dk, M, sp.kv_rank, sp.dim, 0, sp.heads * Dk, 0.f, xa)));
+        } else MX(mx::head_gemm(st, dt, ga, lc));
         if (w.scores && kc->v[l]) {
           // blocks of lat_tok tokens x heads rows: scores = qa . cache^T on the keys the block's last token sees, softmax with
           // the causal mask into w_hi | w_lo, lat = [w_hi | w_lo] . latent^T with the latent's k coordinate wrapping at kp
@@ -1900,7 +1915,13 @@ static int enqueue_mixer_layers(cake_b200_ctx *c, cake_b200_block *const *blocks
         // the weighted latent through the value expansion: att[m, h, :] = uv[h] lat[m, h]   (uv[h]: [vdim, rank])
         mx::HeadGemm gv{w.lat, b->m_uv, w.att, M, sp.vdim, sp.kv_rank, sp.heads, sp.kv_rank, (long)sp.vdim * sp.kv_rank, sp.vdim,
                         sp.heads * sp.kv_rank, sp.kv_rank, inner, 0};
-        MX(mx::head_gemm(st, dt, gv, lc));
+        if (heads_tc) {
+          TcExtra xa;
+          xa.a_ld = sp.heads * sp.kv_rank;
+          for (int hh = 0; hh < sp.heads; hh++)
+            RC((listed_gemm_tc<T, TCE_PLAIN>(c, (const T *)w.lat + (size_t)hh * sp.kv_rank, (const T *)b->m_uv + (size_t)hh * sp.vdim * sp.kv_rank, nullptr,
+                                             (T *)w.att + (size_t)hh * sp.vdim, M, sp.vdim, sp.kv_rank, 0, inner, 0.f, xa)));
+        } else MX(mx::head_gemm(st, dt, gv, lc));
       } else if (sp.kind == CAKE_B200_MIX_RETENTION) {
         const int qk = sp.heads * sp.dim;
         const T *pj = (const T *)w.proj;

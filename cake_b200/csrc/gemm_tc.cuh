@@ -46,8 +46,8 @@ struct TcParams {
   void *C;               // [M,N] D  ([M,N/2] for TCE_SWIGLU)
   int M, N, K;
   int act;  // TCE_SWIGLU: 0 silu, 1 gelu_tanh
-  int ldc;  // TCE_SWIGLU: row stride of C in elements when it is a column range of a wider buffer (0 = N/2; a multiple of 8,
-            // like the column offset folded into C)
+  int ldc;  // TCE_SWIGLU / TCE_PLAIN: row stride of C in elements when it is a column range of a wider buffer (0 = N/2 resp. N;
+            // a multiple of 8, like the column offset folded into C)
   float cap; // TCE_SOFTCAP_F32
   // grouped product (a routed feed-forward): the rows of A are sorted by group in blocks of TC_BM rows, tile_group[m0 / TC_BM]
   // names the group of a row block (< 0: the block is empty and skipped), and group g multiplies by rows g * N .. g * N + N - 1
@@ -316,7 +316,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
           } else {
             uint32_t o[16];
-            const size_t off = (size_t)row * p.N + n0 + c0;
+            const size_t off = (size_t)row * (p.ldc ? p.ldc : p.N) + n0 + c0;  // TCE_PLAIN may write a column range of a wider buffer
             uint32_t rr[16];  // the residual row segment as four 16-byte loads (scalar 2-byte loads made this epilogue longer
                               // than a K=4096 main loop: ncu r02, o_proj 68 % tensor-pipe active against 88-91 % elsewhere)
             if (EPI == TCE_RESIDUAL) {

@@ -344,6 +344,23 @@ int head_gemm(cudaStream_t st, int dtype, const HeadGemm &p, uint64_t *launches)
   MX_DONE(1);
 }
 
+template <typename T>
+__global__ void transpose_batched_kernel(const T *__restrict__ in, T *__restrict__ out, int rows, int cols) {
+  __shared__ T tile[32][33];
+  const size_t z = blockIdx.z;
+  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  for (int i = threadIdx.y; i < 32; i += blockDim.y)
+    if (r0 + i < rows && c0 + (int)threadIdx.x < cols) tile[i][threadIdx.x] = in[(z * rows + r0 + i) * cols + c0 + threadIdx.x];
+  __syncthreads();
+  for (int i = threadIdx.y; i < 32; i += blockDim.y)
+    if (c0 + i < cols && r0 + (int)threadIdx.x < rows) out[(z * cols + c0 + i) * rows + r0 + threadIdx.x] = tile[threadIdx.x][i];
+}
+int transpose_batched(cudaStream_t st, int dtype, const void *in, void *out, int Z, int rows, int cols, uint64_t *launches) {
+  const dim3 grid((cols + 31) / 32, (rows + 31) / 32, Z), block(32, 8);
+  MX_DISPATCH(dtype, (transpose_batched_kernel<T><<<grid, block, 0, st>>>(reinterpret_cast<const T *>(in), reinterpret_cast<T *>(out), rows, cols)));
+  MX_DONE(1);
+}
+
 // ---------------------------------------------------------------------------------------------- gated linear recurrence
 // One CTA per (head, batch row) walks the step's tokens in order.  The state sits in shared memory; thread (j, s) owns
 // column j of the rows i = s, s + RS, ...: it updates them and adds S[i][j] q[i] to its partial of o[j].
@@ -414,7 +431,7 @@ __global__ void recurrence_kernel(const Recurrence p) {
 // registers.  Tokens come in chunks of 16: their q, k (rotated, scaled) and v are staged in shared memory once, the 16 updates
 // run without a barrier, and the eight warps' partial outputs are added up once per chunk.
 constexpr int RC_TT = 16, RC_CB = 32, RC_RS = 8;
-template <typename T, int R>
+template <typename T, int R, bool ROPE>
 __global__ void __launch_bounds__(256) recurrence_cols_kernel(const Recurrence p) {
   extern __shared__ float sm[];
   constexpr int dk = R * RC_RS;
@@ -429,6 +446,41 @@ __global__ void __launch_bounds__(256) recurrence_cols_kernel(const Recurrence p
   const T *dtb = reinterpret_cast<const T *>(p.dt_bias), *alog = reinterpret_cast<const T *>(p.a_log), *skp = reinterpret_cast<const T *>(p.skip);
   const float nexpA = p.dt ? -expf(DT<T>::to_f(alog[h])) : 0.f, bias = p.dt ? DT<T>::to_f(dtb[h]) : 0.f;
   const float skip = skp ? DT<T>::to_f(skp[h]) : 0.f;
+  // Raw values of the next chunk wait in registers while the current one is computed: (R + 1) / 2 q / k entries (with their
+  // rotation partners and table entries), two v entries and one dt per thread.  The loads are straight-line code (indices are
+  // clamped, nothing is selected on a loaded value before the chunk is staged), so that they are all in flight at once.
+  constexpr int NE = (R + 1) / 2;
+  T rq[NE], rqp[NE], rk[NE], rkp[NE], rv[2], rdt = DT<T>::from_f(0.f);
+  float rc[NE], rsn[NE];
+  const T *dtp = reinterpret_cast<const T *>(p.dt ? p.dt : p.v);  // any valid address when there is no dt
+  const int lddt = p.dt ? p.lddt : 0, dth = p.dt ? h : 0;
+  auto fetch = [&](int t0) {
+    const int nt = min(RC_TT, p.S - t0);
+    const size_t m0 = (size_t)b * p.S + t0;
+#pragma unroll
+    for (int e = 0; e < NE; e++) {
+      const int idx = min((int)threadIdx.x + 256 * e, nt * dk - 1), tt = idx / dk, i = idx % dk;
+      const T *qr = reinterpret_cast<const T *>(p.q) + (m0 + tt) * p.ldq + gcol;
+      const T *kr = reinterpret_cast<const T *>(p.k) + (m0 + tt) * p.ldk + gcol;
+      rq[e] = qr[i];
+      rk[e] = kr[i];
+      if (ROPE) {
+        const bool rot = i < p.rope_dims;
+        const int ip = rot ? (i < half ? i + half : i - half) : i, it = rot ? (i < half ? i : i - half) : 0;
+        rqp[e] = qr[ip];
+        rkp[e] = kr[ip];
+        rc[e] = p.cos_t[(size_t)(p.pos0 + t0 + tt) * half + it];
+        rsn[e] = p.sin_t[(size_t)(p.pos0 + t0 + tt) * half + it];
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 2; e++) {
+      const int idx = min((int)threadIdx.x + 256 * e, nt * RC_CB - 1);
+      rv[e] = reinterpret_cast<const T *>(p.v)[(m0 + idx / RC_CB) * p.ldv + (size_t)h * p.dv + cb * RC_CB + idx % RC_CB];
+    }
+    rdt = dtp[(m0 + min((int)threadIdx.x, nt - 1)) * lddt + dth];
+  };
+  fetch(0);
   for (int t0 = 0; t0 < p.S; t0 += RC_TT) {
     const int nt = min(RC_TT, p.S - t0);
     const size_t m0 = (size_t)b * p.S + t0;
@@ -436,54 +488,59 @@ __global__ void __launch_bounds__(256) recurrence_cols_kernel(const Recurrence p
     if ((int)threadIdx.x < nt) {
       float a = p.decay ? p.decay[h] : 1.f, bsc = p.kscale;
       if (p.dt) {
-        const float d = softplus_f(DT<T>::to_f(reinterpret_cast<const T *>(p.dt)[(m0 + threadIdx.x) * p.lddt + h]) + bias);
+        const float d = softplus_f(DT<T>::to_f(rdt) + bias);
         a = expf(nexpA * d);
         bsc = d;
       }
       as[threadIdx.x] = a;
       bs[threadIdx.x] = bsc;
     }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < nt * dk; idx += 256) {
-      const int tt = idx / dk, i = idx % dk;
-      const T *qr = reinterpret_cast<const T *>(p.q) + (m0 + tt) * p.ldq + gcol;
-      const T *kr = reinterpret_cast<const T *>(p.k) + (m0 + tt) * p.ldk + gcol;
-      if (p.cos_t) {
-        const float *cs = p.cos_t + (size_t)(p.pos0 + t0 + tt) * half, *sn = p.sin_t + (size_t)(p.pos0 + t0 + tt) * half;
-        qs[idx] = rotated<T>(qr, i, p.rope_dims, cs, sn);
-        ks[idx] = rotated<T>(kr, i, p.rope_dims, cs, sn) * bs[tt];
-      } else {
-        qs[idx] = DT<T>::to_f(qr[i]);
-        ks[idx] = DT<T>::to_f(kr[i]) * bs[tt];
+#pragma unroll
+    for (int e = 0; e < NE; e++) {
+      const int idx = threadIdx.x + 256 * e;
+      if (idx < nt * dk) {
+        float qv = DT<T>::to_f(rq[e]), kv = DT<T>::to_f(rk[e]);
+        if (ROPE) {  // entry i of a rotated pair: x_i cos - x_partner sin (first half), x_i cos + x_partner sin (second half)
+          const int i = idx % dk;
+          if (i < p.rope_dims) {
+            const float sn = i < half ? -rsn[e] : rsn[e];
+            qv = fmaf(DT<T>::to_f(rqp[e]), sn, qv * rc[e]);
+            kv = fmaf(DT<T>::to_f(rkp[e]), sn, kv * rc[e]);
+          }
+        }
+        qs[idx] = qv;
+        ks[idx] = kv;
       }
     }
-    for (int idx = threadIdx.x; idx < nt * RC_CB; idx += 256) {
-      const int tt = idx / RC_CB, j = idx % RC_CB;
-      vs[idx] = DT<T>::to_f(reinterpret_cast<const T *>(p.v)[(m0 + tt) * p.ldv + (size_t)h * p.dv + cb * RC_CB + j]);
+#pragma unroll
+    for (int e = 0; e < 2; e++) {
+      const int idx = threadIdx.x + 256 * e;
+      if (idx < nt * RC_CB) vs[idx] = DT<T>::to_f(rv[e]);
     }
     __syncthreads();
+    if (t0 + RC_TT < p.S) fetch(t0 + RC_TT);  // in flight while this chunk is computed
     for (int tt = 0; tt < nt; tt++) {
-      const float a = as[tt], v = vs[tt * RC_CB + lane];
+      const float a = as[tt], v = vs[tt * RC_CB + lane] * bs[tt];
       const float *kq = ks + tt * dk + s * R, *qq = qs + tt * dk + s * R;
-      float acc = 0.f;
+      float acc0 = 0.f, acc1 = 0.f;
       if (R % 4 == 0) {
 #pragma unroll
         for (int r = 0; r < R; r += 4) {
           const float4 k4 = *reinterpret_cast<const float4 *>(kq + r), q4 = *reinterpret_cast<const float4 *>(qq + r);
-          St[r] = fmaf(a, St[r], k4.x * v); acc = fmaf(St[r], q4.x, acc);
-          St[r + 1] = fmaf(a, St[r + 1], k4.y * v); acc = fmaf(St[r + 1], q4.y, acc);
-          St[r + 2] = fmaf(a, St[r + 2], k4.z * v); acc = fmaf(St[r + 2], q4.z, acc);
-          St[r + 3] = fmaf(a, St[r + 3], k4.w * v); acc = fmaf(St[r + 3], q4.w, acc);
+          St[r] = fmaf(a, St[r], k4.x * v); acc0 = fmaf(St[r], q4.x, acc0);
+          St[r + 1] = fmaf(a, St[r + 1], k4.y * v); acc1 = fmaf(St[r + 1], q4.y, acc1);
+          St[r + 2] = fmaf(a, St[r + 2], k4.z * v); acc0 = fmaf(St[r + 2], q4.z, acc0);
+          St[r + 3] = fmaf(a, St[r + 3], k4.w * v); acc1 = fmaf(St[r + 3], q4.w, acc1);
         }
       } else {
 #pragma unroll
         for (int r = 0; r < R; r += 2) {
           const float2 k2 = *reinterpret_cast<const float2 *>(kq + r), q2 = *reinterpret_cast<const float2 *>(qq + r);
-          St[r] = fmaf(a, St[r], k2.x * v); acc = fmaf(St[r], q2.x, acc);
-          St[r + 1] = fmaf(a, St[r + 1], k2.y * v); acc = fmaf(St[r + 1], q2.y, acc);
+          St[r] = fmaf(a, St[r], k2.x * v); acc0 = fmaf(St[r], q2.x, acc0);
+          St[r + 1] = fmaf(a, St[r + 1], k2.y * v); acc1 = fmaf(St[r + 1], q2.y, acc1);
         }
       }
-      part[(s * RC_TT + tt) * RC_CB + lane] = acc;
+      part[(s * RC_TT + tt) * RC_CB + lane] = acc0 + acc1;
     }
     __syncthreads();
     for (int idx = threadIdx.x; idx < nt * RC_CB; idx += 256) {
@@ -497,15 +554,18 @@ __global__ void __launch_bounds__(256) recurrence_cols_kernel(const Recurrence p
 #pragma unroll
   for (int r = 0; r < R; r++) gstate[(size_t)r * p.dv] = St[r];
 }
-template <typename T, int R> static cudaError_t launch_recurrence_cols(cudaStream_t st, const Recurrence &p) {
+template <typename T, int R, bool ROPE> static cudaError_t launch_recurrence_cols2(cudaStream_t st, const Recurrence &p) {
   constexpr int dk = R * RC_RS;
   const size_t smem = (size_t)(2 * RC_TT * dk + RC_TT * RC_CB + 2 * RC_TT + RC_RS * RC_TT * RC_CB) * sizeof(float);
   if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(recurrence_cols_kernel<T, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(recurrence_cols_kernel<T, R, ROPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
   }
-  recurrence_cols_kernel<T, R><<<dim3(p.heads * (p.dv / RC_CB), p.B), 256, smem, st>>>(p);
+  recurrence_cols_kernel<T, R, ROPE><<<dim3(p.heads * (p.dv / RC_CB), p.B), 256, smem, st>>>(p);
   return cudaSuccess;
+}
+template <typename T, int R> static cudaError_t launch_recurrence_cols(cudaStream_t st, const Recurrence &p) {
+  return p.cos_t && p.rope_dims > 0 ? launch_recurrence_cols2<T, R, true>(st, p) : launch_recurrence_cols2<T, R, false>(st, p);
 }
 
 int recurrence(cudaStream_t st, int dtype, const Recurrence &p, uint64_t *launches) {
@@ -547,7 +607,7 @@ __global__ void __launch_bounds__(256) short_conv_kernel(const ShortConv p) {
   const T *w = reinterpret_cast<const T *>(p.w), *bias = reinterpret_cast<const T *>(p.bias);
   const T *hist = reinterpret_cast<const T *>(p.hist) + (size_t)b * back * p.channels;
   T *out = reinterpret_cast<T *>(p.out) + (size_t)m * p.channels;
-  for (int ch = threadIdx.x; ch < p.channels; ch += blockDim.x) {
+  for (int ch = blockIdx.y * blockDim.x + threadIdx.x; ch < p.channels; ch += gridDim.y * blockDim.x) {
     float acc = DT<T>::to_f(bias[ch]);
     for (int jt = 0; jt < p.taps; jt++) {
       const int tt = t - back + jt;
@@ -558,6 +618,76 @@ __global__ void __launch_bounds__(256) short_conv_kernel(const ShortConv p) {
     }
     out[ch] = DT<T>::from_f(silu_f(acc));
   }
+}
+// 16-bit D with channel counts, strides and offsets that are multiples of 8: a thread owns eight channels, keeps their
+// TAPS x 8 weights and a sliding window of inputs in registers and walks SC_TOK tokens, so that a row is read once
+constexpr int SC_TOK = 16;
+template <typename T, int TAPS>
+__global__ void __launch_bounds__(128) short_conv_vec_kernel(const ShortConv p) {
+  const int c8 = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c8 >= p.channels / 8) return;
+  const int ch = c8 * 8, chunks = (p.S + SC_TOK - 1) / SC_TOK, b = blockIdx.x / chunks, t0 = (blockIdx.x % chunks) * SC_TOK;
+  const T *in = reinterpret_cast<const T *>(p.in) + (size_t)b * p.S * p.ld + p.col0 + ch;
+  const T *hist = reinterpret_cast<const T *>(p.hist) + (size_t)b * (TAPS - 1) * p.channels + ch;
+  T *out = reinterpret_cast<T *>(p.out) + (size_t)b * p.S * p.channels + ch;
+  float w[8][TAPS], bias[8], x[TAPS][8];
+  {
+    const uint4 *w4 = reinterpret_cast<const uint4 *>(reinterpret_cast<const T *>(p.w) + (size_t)ch * TAPS);  // 8 * TAPS contiguous weights
+    float tmp[8 * TAPS];
+#pragma unroll
+    for (int i = 0; i < TAPS; i++) {
+      float f[8];
+      unpack8<T>(w4[i], f);
+#pragma unroll
+      for (int e = 0; e < 8; e++) tmp[8 * i + e] = f[e];
+    }
+#pragma unroll
+    for (int e = 0; e < 8; e++)
+#pragma unroll
+      for (int jt = 0; jt < TAPS; jt++) w[e][jt] = tmp[e * TAPS + jt];
+    unpack8<T>(*reinterpret_cast<const uint4 *>(reinterpret_cast<const T *>(p.bias) + ch), bias);
+  }
+#pragma unroll
+  for (int jt = 0; jt < TAPS - 1; jt++) {  // the rows before the chunk: this step's, the history's, or zeros before position 0
+    const int tt = t0 - (TAPS - 1) + jt;
+    if (tt >= 0) unpack8<T>(*reinterpret_cast<const uint4 *>(in + (size_t)tt * p.ld), x[jt]);
+    else if (p.pos0 > 0) unpack8<T>(*reinterpret_cast<const uint4 *>(hist + (size_t)(TAPS - 1 + tt) * p.channels), x[jt]);
+    else {
+#pragma unroll
+      for (int e = 0; e < 8; e++) x[jt][e] = 0.f;
+    }
+  }
+  const int t1 = min(p.S, t0 + SC_TOK);
+  for (int t = t0; t < t1; t++) {
+    unpack8<T>(*reinterpret_cast<const uint4 *>(in + (size_t)t * p.ld), x[TAPS - 1]);
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; e++) {
+      acc[e] = bias[e];
+#pragma unroll
+      for (int jt = 0; jt < TAPS; jt++) acc[e] = fmaf(w[e][jt], x[jt][e], acc[e]);
+    }
+    uint4 o;
+    o.x = pack2x<T>(silu_f(acc[0]), silu_f(acc[1])); o.y = pack2x<T>(silu_f(acc[2]), silu_f(acc[3]));
+    o.z = pack2x<T>(silu_f(acc[4]), silu_f(acc[5])); o.w = pack2x<T>(silu_f(acc[6]), silu_f(acc[7]));
+    *reinterpret_cast<uint4 *>(out + (size_t)t * p.channels) = o;
+#pragma unroll
+    for (int jt = 0; jt < TAPS - 1; jt++)
+#pragma unroll
+      for (int e = 0; e < 8; e++) x[jt][e] = x[jt + 1][e];
+  }
+}
+template <typename T> static void launch_short_conv(cudaStream_t st, const ShortConv &p) {
+  const bool vec = p.channels % 8 == 0 && p.ld % 8 == 0 && p.col0 % 8 == 0 && p.taps >= 2 && p.taps <= 4 &&
+                   (((uintptr_t)p.in | (uintptr_t)p.hist | (uintptr_t)p.out | (uintptr_t)p.bias | (uintptr_t)p.w) & 15) == 0;
+  const dim3 gv(p.B * ((p.S + SC_TOK - 1) / SC_TOK), (p.channels / 8 + 127) / 128);
+  if (vec && p.taps == 2) short_conv_vec_kernel<T, 2><<<gv, 128, 0, st>>>(p);
+  else if (vec && p.taps == 3) short_conv_vec_kernel<T, 3><<<gv, 128, 0, st>>>(p);
+  else if (vec && p.taps == 4) short_conv_vec_kernel<T, 4><<<gv, 128, 0, st>>>(p);
+  else short_conv_kernel<T><<<dim3(p.B * p.S, (p.channels + 255) / 256), 256, 0, st>>>(p);
+}
+template <> void launch_short_conv<float>(cudaStream_t st, const ShortConv &p) {
+  short_conv_kernel<float><<<dim3(p.B * p.S, (p.channels + 255) / 256), 256, 0, st>>>(p);
 }
 // after the convolution: the history becomes the last taps - 1 inputs up to the end of this step (zeros before position 0)
 template <typename T>
@@ -577,7 +707,7 @@ __global__ void short_conv_hist_kernel(const ShortConv p) {
 }
 int short_conv(cudaStream_t st, int dtype, const ShortConv &p, uint64_t *launches) {
   MX_DISPATCH(dtype, {
-    short_conv_kernel<T><<<p.B * p.S, 256, 0, st>>>(p);
+    launch_short_conv<T>(st, p);
     if (p.taps > 1) short_conv_hist_kernel<T><<<(p.B * p.channels + 255) / 256, 256, 0, st>>>(p);
   });
   MX_DONE(p.taps > 1 ? 2 : 1);
@@ -675,16 +805,24 @@ __global__ void moe_count_kernel(const int *ids, int n, int experts, int *counts
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n && ids[i] < experts) atomicAdd(&counts[ids[i]], 1);
 }
-// one thread: every expert's pairs start on a multiple of `tile` sorted rows; counts[e] becomes that start (the scatter's cursor)
+// one warp: every expert's pairs start on a multiple of `tile` sorted rows; counts[e] becomes that start (the scatter's cursor)
 __global__ void moe_tiles_kernel(const MoePlan p) {
-  if (threadIdx.x != 0 || blockIdx.x != 0) return;
-  int nt = 0;
-  for (int e = 0; e < p.experts; e++) {
-    const int cnt = p.counts[e];
-    p.counts[e] = nt * p.tile;
-    for (int r = 0; r < cnt && nt < p.max_tiles; r += p.tile) p.tile_expert[nt++] = e;
+  const int lane = threadIdx.x;
+  int done = 0;  // blocks of `tile` rows handed out so far
+  for (int base = 0; base < p.experts; base += 32) {
+    const int e = base + lane, cnt = e < p.experts ? p.counts[e] : 0, nt = (cnt + p.tile - 1) / p.tile;
+    int incl = nt;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    const int first = done + incl - nt;
+    if (e < p.experts) p.counts[e] = first * p.tile;
+    for (int i = 0; i < nt && first + i < p.max_tiles; i++) p.tile_expert[first + i] = e;
+    done += __shfl_sync(0xffffffffu, incl, 31);
   }
-  for (; nt < p.max_tiles; nt++) p.tile_expert[nt] = -1;
+  for (int i = done + lane; i < p.max_tiles; i += 32) p.tile_expert[i] = -1;
 }
 __global__ void moe_scatter_kernel(const int *ids, int n, int experts, int *cursor, int *perm, int *pos_of) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -820,7 +958,7 @@ template <typename T>
 __global__ void __launch_bounds__(256) moe_combine_kernel(const MoeCombine p) {
   const int m = blockIdx.x;
   const T *h = reinterpret_cast<const T *>(p.h) + (size_t)m * p.W;
-  for (int i = threadIdx.x; i < p.W; i += blockDim.x) {
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < p.W; i += gridDim.y * blockDim.x) {
     float s = 0.f;
     for (int k = 0; k < p.top; k++) {
       const size_t pr = (size_t)m * p.top + k;
@@ -831,7 +969,7 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const MoeCombine p) {
   }
 }
 int moe_combine(cudaStream_t st, int dtype, const MoeCombine &p, uint64_t *launches) {
-  MX_DISPATCH(dtype, (moe_combine_kernel<T><<<p.M, 256, 0, st>>>(p)));
+  MX_DISPATCH(dtype, (moe_combine_kernel<T><<<dim3(p.M, p.M < 64 ? (p.W + 255) / 256 : 1), 256, 0, st>>>(p)));
   MX_DONE(1);
 }
 

@@ -70,6 +70,9 @@ struct HeadGemm {
 };
 int head_gemm(cudaStream_t, int dtype, const HeadGemm &, uint64_t *launches);
 
+// out[z][c][r] = in[z][r][c] for Z matrices of [rows, cols] in D (weight layouts for the tensor-core products, at load)
+int transpose_batched(cudaStream_t, int dtype, const void *in, void *out, int Z, int rows, int cols, uint64_t *launches);
+
 // ---- gated linear recurrence -----------------------------------------------------------------------------------------
 //   S_t = a_t S_{t-1} + b_t k_t v_t^T   (S: [dk, dv] fp32 per batch row and head),   o_t = S_t^T q_t + skip_h v_t
 // fixed decay:      a_t = decay[h], b_t = kscale           (dt == nullptr)
