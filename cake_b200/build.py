@@ -51,7 +51,8 @@ def _unit_stale(obj: str, src: str, deps) -> bool:
     if not os.path.exists(obj):
         return True
     t = os.path.getmtime(obj)
-    files = sources() if deps is None else [os.path.join(d, src)] + [os.path.join(d, x) for x in deps]
+    others = {os.path.join(d, s_) for _, (s_, _) in UNITS.items() if s_ != src}   # another unit's .cu is not a dependency
+    files = [f for f in sources() if f not in others] if deps is None else [os.path.join(d, src)] + [os.path.join(d, x) for x in deps]
     return any(os.path.getmtime(f) > t for f in files)
 
 

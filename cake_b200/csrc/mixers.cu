@@ -432,7 +432,7 @@ __global__ void recurrence_kernel(const Recurrence p) {
 // run without a barrier, and the eight warps' partial outputs are added up once per chunk.
 constexpr int RC_TT = 16, RC_CB = 32, RC_RS = 8;
 template <typename T, int R, bool ROPE>
-__global__ void __launch_bounds__(256) recurrence_cols_kernel(const Recurrence p) {
+__global__ void __launch_bounds__(256, R > 16 ? 1 : (ROPE ? 2 : 3)) recurrence_cols_kernel(const Recurrence p) {
   extern __shared__ float sm[];
   constexpr int dk = R * RC_RS;
   float *qs = sm, *ks = qs + RC_TT * dk, *vs = ks + RC_TT * dk, *as = vs + RC_TT * RC_CB, *bs = as + RC_TT, *part = bs + RC_TT;
