@@ -193,6 +193,13 @@ MECHANISMS = {
     "moe": lambda: make_config([retention(moe=moe())]),
     "moe_identity_only_choice": lambda: make_config([retention(moe=moe(experts=2, identity=3, top=4, shared_ff=0))]),
     "moe_top1_no_identity": lambda: make_config([mamba(moe=moe(experts=6, identity=0, top=1, ff=8, shared_ff=16))]),
+    "moe_many_experts": lambda: make_config([retention(moe=moe(experts=40, identity=3, top=5, ff=8, shared_ff=16))]),
+    "state_space_key_size_48": lambda: make_config([mamba(heads=2, vdim=32, state=48, groups=1, conv=3, norm_groups=2)]),
+    "state_space_key_size_256": lambda: make_config([mamba(heads=1, vdim=64, state=256, groups=1, conv=2, norm_groups=1)]),
+    "retention_key_size_96": lambda: make_config([retention(heads=2, dim=96, vdim=32, rot_dims=64, decay=[0.9, 0.99])]),
+    "retention_key_size_128": lambda: make_config([retention(heads=1, dim=128, vdim=64, rot_dims=128, decay=[0.98])]),
+    "retention_key_size_192": lambda: make_config([retention(heads=1, dim=192, vdim=32, rot_dims=32, decay=[0.95])]),
+    "latent_rank_400": lambda: make_config([latent(heads=2, dim=8, rot_dim=16, vdim=8, kv_rank=400, scale=0.3)]),
     "loop_from_layer0": lambda: make_config([retention(), latent()], loop={"start": 0, "stop": 2, "times": 3}),
     "loop_once_tail_only": lambda: make_config([mamba(), retention()], loop={"start": 1, "stop": 2, "times": 1}),
     "no_embedding_scale": lambda: make_config([latent(moe=moe())], embed_scale=1.0),
