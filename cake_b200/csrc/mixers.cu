@@ -240,12 +240,16 @@ __global__ void __launch_bounds__(128) latent_softmax_kernel(const LatentSoftmax
   const int t = (int)(row / p.heads), n_keys = min(p.kp, p.pos_first + t + 1);
   const float *s = p.scores + (size_t)row * p.kp;
   T *w = reinterpret_cast<T *>(p.w) + (size_t)row * 2 * p.kp;
-  float mx = -INFINITY;
-  for (int j = lane; j < n_keys; j += 32) mx = fmaxf(mx, s[j]);
-  mx = warp_max(mx) * p.scale;
-  float l = 0.f;
-  for (int j = lane; j < n_keys; j += 32) l += expf(fmaf(s[j], p.scale, -mx));
-  l = warp_sum(l);
+  float mxl = -INFINITY, ll = 0.f;  // one read: every lane keeps a running maximum and the sum relative to it
+  for (int j = lane; j < n_keys; j += 32) {
+    const float v = s[j] * p.scale;
+    if (v > mxl) {
+      ll = ll * expf(mxl - v) + 1.f;
+      mxl = v;
+    } else ll += expf(v - mxl);
+  }
+  const float mx = warp_max(mxl);
+  const float l = warp_sum(mxl == -INFINITY ? 0.f : ll * expf(mxl - mx));
   const float il = 1.0f / l;
   for (int j = lane; j < p.kp; j += 32) {
     const float pr = j < n_keys ? expf(fmaf(s[j], p.scale, -mx)) * il : 0.f;
@@ -338,7 +342,44 @@ __global__ void __launch_bounds__(256) head_gemm_kernel(const HeadGemm p) {
     }
   }
 }
+// Steps of a few rows: no tiles.  w_kn (W[z] stored [K, N]): a thread per output column walks k with coalesced loads;
+// else (W[z] stored [N, K]): a warp per output column splits k.  The row of A sits in shared memory.
+template <typename T>
+__global__ void __launch_bounds__(128) head_gemv_kernel(const HeadGemm p) {
+  extern __shared__ float arow[];
+  const int z = blockIdx.z, m = blockIdx.y;
+  const T *A = reinterpret_cast<const T *>(p.A) + (size_t)z * p.a_zs + (size_t)m * p.lda;
+  const T *W = reinterpret_cast<const T *>(p.W) + (size_t)z * p.w_zs;
+  T *C = reinterpret_cast<T *>(p.C) + (size_t)z * p.c_zs + (size_t)m * p.ldc;
+  for (int k = threadIdx.x; k < p.K; k += blockDim.x) arow[k] = DT<T>::to_f(A[k]);
+  __syncthreads();
+  if (p.w_kn) {
+    const int n = blockIdx.x * 128 + threadIdx.x;
+    if (n >= p.N) return;
+    float a0 = 0.f, a1 = 0.f;
+    int k = 0;
+    for (; k + 1 < p.K; k += 2) {
+      a0 = fmaf(arow[k], DT<T>::to_f(W[(size_t)k * p.ldw + n]), a0);
+      a1 = fmaf(arow[k + 1], DT<T>::to_f(W[(size_t)(k + 1) * p.ldw + n]), a1);
+    }
+    if (k < p.K) a0 = fmaf(arow[k], DT<T>::to_f(W[(size_t)k * p.ldw + n]), a0);
+    C[n] = DT<T>::from_f(a0 + a1);
+  } else {
+    const int n = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (n >= p.N) return;
+    const T *w = W + (size_t)n * p.ldw;
+    float acc = 0.f;
+    for (int k = lane; k < p.K; k += 32) acc = fmaf(arow[k], DT<T>::to_f(w[k]), acc);
+    acc = warp_sum(acc);
+    if (lane == 0) C[n] = DT<T>::from_f(acc);
+  }
+}
 int head_gemm(cudaStream_t st, int dtype, const HeadGemm &p, uint64_t *launches) {
+  if (p.M <= 8 && p.K <= 8192) {
+    const dim3 grid(p.w_kn ? (p.N + 127) / 128 : (p.N + 3) / 4, p.M, p.Z);
+    MX_DISPATCH(dtype, (head_gemv_kernel<T><<<grid, 128, (size_t)p.K * sizeof(float), st>>>(p)));
+    MX_DONE(1);
+  }
   dim3 grid((p.N + HG_BN - 1) / HG_BN, (p.M + HG_BM - 1) / HG_BM, p.Z);
   MX_DISPATCH(dtype, (head_gemm_kernel<T><<<grid, 256, 0, st>>>(p)));
   MX_DONE(1);
@@ -832,11 +873,53 @@ __global__ void moe_scatter_kernel(const int *ids, int n, int experts, int *curs
     pos_of[i] = pos;
   }
 }
+// few (token, slot) pairs (decoding): count, plan and scatter in one CTA with the counters in shared memory
+constexpr int MOE_SMALL_PAIRS = 1024;
+__global__ void __launch_bounds__(256) moe_plan_small_kernel(const MoePlan p) {
+  __shared__ int cnt[32 * MOE_MAX_SLOTS];
+  __shared__ int done_s;
+  const int ne = p.M * p.top, rows = p.max_tiles * p.tile;
+  for (int e = threadIdx.x; e < p.experts; e += blockDim.x) cnt[e] = 0;
+  for (int r = threadIdx.x; r < rows; r += blockDim.x) p.perm[r] = -1;
+  __syncthreads();
+  for (int i = threadIdx.x; i < ne; i += blockDim.x)
+    if (p.ids[i] < p.experts) atomicAdd(&cnt[p.ids[i]], 1);
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    int done = 0;
+    for (int base = 0; base < p.experts; base += 32) {
+      const int e = base + lane, c = e < p.experts ? cnt[e] : 0, nt = (c + p.tile - 1) / p.tile;
+      int incl = nt;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+      }
+      const int first = done + incl - nt;
+      if (e < p.experts) cnt[e] = first * p.tile;
+      for (int i = 0; i < nt && first + i < p.max_tiles; i++) p.tile_expert[first + i] = e;
+      done += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) done_s = done;
+  }
+  __syncthreads();
+  for (int i = done_s + threadIdx.x; i < p.max_tiles; i += blockDim.x) p.tile_expert[i] = -1;
+  for (int i = threadIdx.x; i < ne; i += blockDim.x)
+    if (p.ids[i] < p.experts) {
+      const int pos = atomicAdd(&cnt[p.ids[i]], 1);
+      p.perm[pos] = i;
+      p.pos_of[i] = pos;
+    }
+}
 int moe_route(cudaStream_t st, int dtype, const MoePlan &p, uint64_t *launches) {
   if (p.experts + p.identity > 32 * MOE_MAX_SLOTS || p.top > 32 || p.top < 1 || p.top > p.experts + p.identity) return (int)cudaErrorInvalidValue;
   MX_DISPATCH(dtype, (moe_router_kernel<T><<<(p.M + 3) / 4, 128, 0, st>>>(p)));
   int n = 1;
-  if (p.experts > 0) {
+  if (p.experts > 0 && p.M * p.top <= MOE_SMALL_PAIRS) {
+    moe_plan_small_kernel<<<1, 256, 0, st>>>(p);
+    n += 1;
+  } else if (p.experts > 0) {
     cudaMemsetAsync(p.counts, 0, sizeof(int) * (p.experts + 1), st);
     cudaMemsetAsync(p.perm, 0xff, sizeof(int) * (size_t)p.max_tiles * p.tile, st);
     const int ne = p.M * p.top;
