@@ -1587,7 +1587,8 @@ static bool latent_on_tc(const cake_b200_ctx *c, const cake_b200_block *b) {
   return !no_tc && c->cfg.dtype != CAKE_B200_F32 && sp.kind == CAKE_B200_MIX_LATENT && (sp.kv_rank + sp.rot_dim) % TC_BK == 0 && sp.kv_rank % TC_BN == 0;
 }
 static int latent_cap_t(int cap) { return (cap + 63) / 64 * 64; }
-constexpr int LATENT_TC_ROWS = 4096;     // (token, head) rows per block of the matrix-product form
+constexpr int LATENT_TC_ROWS = 4736;     // (token, head) rows per block of the matrix-product form: 37 row tiles x 4 column tiles of the
+                                         // weights-times-latent product at rank 512 = one tile per SM
 constexpr int LATENT_TC_MIN_ROWS = 1024; // shorter steps take the per-row kernels
 constexpr int LATENT_SPLIT_MAX = 32;
 

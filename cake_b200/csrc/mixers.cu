@@ -231,36 +231,65 @@ __global__ void __launch_bounds__(128) latent_attn_merge_kernel(const LatentAttn
   }
 }
 
-// weights of the matrix-product form: one warp per (token, head) row of the block
+template <typename T> __device__ __forceinline__ void store4(T *d, const float (&v)[4]) {
+#pragma unroll
+  for (int e = 0; e < 4; e++) d[e] = DT<T>::from_f(v[e]);
+}
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16 *d, const float (&v)[4]) {
+  *reinterpret_cast<uint2 *>(d) = make_uint2(pack2x<__nv_bfloat16>(v[0], v[1]), pack2x<__nv_bfloat16>(v[2], v[3]));
+}
+template <> __device__ __forceinline__ void store4<__half>(__half *d, const float (&v)[4]) {
+  *reinterpret_cast<uint2 *>(d) = make_uint2(pack2x<__half>(v[0], v[1]), pack2x<__half>(v[2], v[3]));
+}
+// weights of the matrix-product form: one warp per (token, head) row of the block; kp is a multiple of 128, so a lane
+// moves four consecutive scores per load (16 bytes in, 8 + 8 bytes out)
 template <typename T>
 __global__ void __launch_bounds__(128) latent_softmax_kernel(const LatentSoftmax p) {
   const long row = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (row >= (long)p.n_tok * p.heads) return;
   const int t = (int)(row / p.heads), n_keys = min(p.kp, p.pos_first + t + 1);
-  const float *s = p.scores + (size_t)row * p.kp;
+  const float4 *s4 = reinterpret_cast<const float4 *>(p.scores + (size_t)row * p.kp);
   T *w = reinterpret_cast<T *>(p.w) + (size_t)row * 2 * p.kp;
+  const int n4 = (n_keys + 3) / 4;
   float mxl = -INFINITY, ll = 0.f;  // one read: every lane keeps a running maximum and the sum relative to it
-  for (int j = lane; j < n_keys; j += 32) {
-    const float v = s[j] * p.scale;
-    if (v > mxl) {
-      ll = ll * expf(mxl - v) + 1.f;
-      mxl = v;
-    } else ll += expf(v - mxl);
+  for (int j4 = lane; j4 < n4; j4 += 32) {
+    const float4 v4 = s4[j4];
+    const float v[4] = {v4.x * p.scale, v4.y * p.scale, v4.z * p.scale, v4.w * p.scale};
+    float m4 = -INFINITY;
+#pragma unroll
+    for (int e = 0; e < 4; e++)
+      if (4 * j4 + e < n_keys) m4 = fmaxf(m4, v[e]);
+    if (m4 > mxl) {
+      ll *= expf(mxl - m4);
+      mxl = m4;
+    }
+#pragma unroll
+    for (int e = 0; e < 4; e++)
+      if (4 * j4 + e < n_keys) ll += expf(v[e] - mxl);
   }
   const float mx = warp_max(mxl);
   const float l = warp_sum(mxl == -INFINITY ? 0.f : ll * expf(mxl - mx));
   const float il = 1.0f / l;
-  for (int j = lane; j < p.kp; j += 32) {
-    const float pr = j < n_keys ? expf(fmaf(s[j], p.scale, -mx)) * il : 0.f;
-    const T hi = DT<T>::from_f(pr);
-    w[j] = hi;
-    w[p.kp + j] = DT<T>::from_f(pr - DT<T>::to_f(hi));
+  for (int j4 = lane; j4 < p.kp / 4; j4 += 32) {
+    float pr[4] = {0.f, 0.f, 0.f, 0.f};
+    if (j4 < n4) {
+      const float4 v4 = s4[j4];
+      const float v[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+      for (int e = 0; e < 4; e++)
+        if (4 * j4 + e < n_keys) pr[e] = expf(fmaf(v[e], p.scale, -mx)) * il;
+    }
+    float lo[4];
+#pragma unroll
+    for (int e = 0; e < 4; e++) lo[e] = pr[e] - rnd<T>(pr[e]);
+    store4<T>(w + 4 * j4, pr);
+    store4<T>(w + p.kp + 4 * j4, lo);
   }
 }
 int latent_softmax(cudaStream_t st, int dtype, const LatentSoftmax &p, uint64_t *launches) {
   const long warps = (long)p.n_tok * p.heads;
-  if (p.scale <= 0.f) return (int)cudaErrorInvalidValue;  // the row maximum is taken before scaling
+  if (p.kp % 4) return (int)cudaErrorInvalidValue;
   MX_DISPATCH(dtype, (latent_softmax_kernel<T><<<(unsigned)((warps + 3) / 4), 128, 0, st>>>(p)));
   MX_DONE(1);
 }
