@@ -404,3 +404,40 @@ def test_greedy_generation_through_master():
         assert lg[tok] >= lg.max() - 1e-2 * np.abs(lg).max(), (len(seq), tok, int(lg.argmax()))   # the sampler reads 16-bit logits
         seq.append(tok)
     assert len(out) == 12
+
+
+@pytest.mark.gpu
+def test_checkpoint_on_disk_through_the_trace_replayer_and_the_generate_command(tmp_path):
+    """config.json + model.safetensors on disk -> `bin/trace_run` (steps on standard input, logits as files) and
+    `python -m cake_b200.run` (token ids out): the model class follows the config in both."""
+    import os
+    import subprocess
+    import sys
+    from cake_b200.loader import open_model, save_checkpoint
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = full_config(max_seq=64)
+    sd = make_mixer_checkpoint(cfg, "bf16", seed=81)
+    model_dir, out_dir = str(tmp_path / "model"), str(tmp_path / "out")
+    save_checkpoint(model_dir, cfg, sd)
+    back, vb = open_model(model_dir)
+    assert back.layers == cfg.layers and back.loop == cfg.loop and set(vb.keys()) == set(sd.keys())
+    toks = tokens(21, cfg.vocab_size, seed=14)
+    want = plain(cfg, sd, toks)
+    steps = [{"step": 0, "entries": [{"id": "r", "tokens": toks[:9], "want": [0, 8]}], "end": []},
+             {"step": 1, "entries": [{"id": "r", "tokens": toks[9:11], "want": []}], "end": []},
+             {"step": 2, "entries": [{"id": "r", "tokens": toks[11:], "want": [9]}], "end": ["r"]},
+             {"step": 3, "entries": [{"id": "s", "tokens": toks[:4], "want": [3]}], "end": ["s"]}]
+    for dtype in ("float32", "bfloat16"):
+        res = subprocess.run([os.path.join(root, "bin", "trace_run"), "--model", model_dir, "--dtype", dtype, "--out", out_dir, "--max-tokens", "40"],
+                             input="".join(json.dumps(x) + "\n" for x in steps), capture_output=True, text=True, timeout=900)
+        assert res.returncode == 0, res.stderr[-2000:]
+        assert [ln for ln in res.stdout.splitlines() if ln.startswith("done")] == ["done 0", "done 1", "done 2", "done 3"]
+        assert not os.path.exists(os.path.join(out_dir, "1.f32"))
+        got = {i: np.fromfile(os.path.join(out_dir, f"{i}.f32"), dtype="<f4").reshape(-1, cfg.vocab_size) for i in (0, 2, 3)}
+        short = "f32" if dtype == "float32" else "bf16"
+        close(np.concatenate([got[0], got[2], got[3]]), want[[0, 8, 20, 3]], short, f"trace replay in {dtype}")
+    res = subprocess.run([sys.executable, "-m", "cake_b200.run", model_dir, "--prompt-ids", ",".join(map(str, toks[:6])), "-n", "5", "--dtype", "f32"],
+                         capture_output=True, text=True, timeout=900, cwd=root)
+    assert res.returncode == 0, res.stderr[-2000:]
+    out = [int(t) for t in res.stdout.split("tokens:")[1].splitlines()[0].split()]
+    assert len(out) == 5 and all(0 <= t < cfg.vocab_size for t in out)
