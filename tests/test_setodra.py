@@ -309,6 +309,33 @@ def test_interleaved_requests_and_reused_slots():
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_batch_rows_against_each_alone(dtype):
+    """Three equal-length rows in one call (a prompt portion, a second portion, then single tokens) give what each row gives
+    alone: cache rows, recurrent state, convolution history and expert plans are per batch row."""
+    from cake_b200.model import Cache
+    cfg = full_config()
+    sd = make_mixer_checkpoint(cfg, dtype, seed=91)
+    rows = [tokens(40, cfg.vocab_size, seed=20 + i) for i in range(3)]
+    want = np.stack([plain(cfg, sd, r) for r in rows])          # [3, 40, vocab]
+    r = Runner(cfg, sd, dtype)
+    try:
+        ctx, model = r.ctx, r.model
+        ctx.cache = Cache(ctx, 3, cfg.max_seq_len)
+        got, pos = [[] for _ in rows], 0
+        for n in (23, 9, 1, 1, 6):
+            ids = np.array([row[pos:pos + n] for row in rows], dtype=np.uint32)
+            lg = model.forward(ids, pos, want=list(range(3 * n))).cpu().numpy().reshape(3, n, -1)
+            for b in range(3):
+                got[b].append(lg[b])
+            pos += n
+        for b in range(3):
+            close(np.concatenate(got[b]), want[b], dtype, f"batch row {b}")
+    finally:
+        r.close()
+
+
+@pytest.mark.gpu
 def test_far_key_in_prompt_portions_and_decoding():
     """A sharp latent attention (one key dominates each row, most of them far back) over a few hundred positions: whole,
     in portions, and with the tail decoded token by token.  That the far keys matter is checked on the plain model itself:
@@ -383,6 +410,15 @@ def test_long_portions_on_the_tensor_cores():
         small = r.run("s", toks, cuts=[100])       # every portion below the matrix-product threshold
         close(small, want, "bf16", "short portions")
         assert np.quantile(errors(whole, small), 0.95) < TOL["bf16"]
+        # two batch rows through the same long-portion kernels, then a second portion on top
+        from cake_b200.model import Cache
+        a, b = toks[:340], toks[340:680]
+        wa, wb = plain(cfg, sd, a), plain(cfg, sd, b)
+        r.ctx.cache = Cache(r.ctx, 2, cfg.max_seq_len)
+        g1 = r.model.forward(np.array([a[:200], b[:200]], dtype=np.uint32), 0, want=list(range(400))).cpu().numpy().reshape(2, 200, -1)
+        g2 = r.model.forward(np.array([a[200:], b[200:]], dtype=np.uint32), 200, want=list(range(280))).cpu().numpy().reshape(2, 140, -1)
+        close(np.concatenate([g1[0], g2[0]]), wa, "bf16", "batch row 0")
+        close(np.concatenate([g1[1], g2[1]]), wb, "bf16", "batch row 1")
     finally:
         r.close()
 
