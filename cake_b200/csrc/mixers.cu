@@ -627,9 +627,13 @@ __global__ void __launch_bounds__(256, R > 16 ? 1 : (ROPE ? 2 : 3)) recurrence_c
 template <typename T, int R, bool ROPE> static cudaError_t launch_recurrence_cols2(cudaStream_t st, const Recurrence &p) {
   constexpr int dk = R * RC_RS;
   const size_t smem = (size_t)(2 * RC_TT * dk + RC_TT * RC_CB + 2 * RC_TT + RC_RS * RC_TT * RC_CB) * sizeof(float);
-  if (smem > 48 * 1024) {
+  static int attr_dev = -1;  // per instantiation: the device the attribute was last set on (the value never changes)
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (smem > 48 * 1024 && attr_dev != dev) {
     cudaError_t e = cudaFuncSetAttribute(recurrence_cols_kernel<T, R, ROPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
+    attr_dev = dev;
   }
   recurrence_cols_kernel<T, R, ROPE><<<dim3(p.heads * (p.dv / RC_CB), p.B), 256, smem, st>>>(p);
   return cudaSuccess;
@@ -662,8 +666,14 @@ int recurrence(cudaStream_t st, int dtype, const Recurrence &p, uint64_t *launch
   const size_t smem = ((size_t)p.dk * p.dv + 2 * p.dk + p.dv + (size_t)RS * p.dv) * sizeof(float);
   if (smem > 227 * 1024) return (int)cudaErrorInvalidValue;
   MX_DISPATCH(dtype, {
-    cudaError_t e = cudaFuncSetAttribute(recurrence_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-    if (e != cudaSuccess) return (int)e;
+    static int attr_dev = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (attr_dev != dev) {
+      cudaError_t e = cudaFuncSetAttribute(recurrence_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+      if (e != cudaSuccess) return (int)e;
+      attr_dev = dev;
+    }
     recurrence_kernel<T><<<dim3(p.heads, p.B), threads, smem, st>>>(p);
   });
   MX_DONE(1);
@@ -784,6 +794,8 @@ int short_conv(cudaStream_t st, int dtype, const ShortConv &p, uint64_t *launche
 }
 
 // ---------------------------------------------------------------------------------------------- gated unit norm
+template <typename T> struct Bits16 { typedef T type; };
+template <> struct Bits16<float> { typedef __nv_bfloat16 type; };  // never taken for float (sizeof test); keeps the vector path instantiable
 template <typename T>
 __global__ void __launch_bounds__(128) gate_norm_kernel(const GateNorm p) {
   const long warp = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -795,6 +807,48 @@ __global__ void __launch_bounds__(128) gate_norm_kernel(const GateNorm p) {
   const T *w = p.w ? reinterpret_cast<const T *>(p.w) + c0 : nullptr;
   T *out = reinterpret_cast<T *>(p.out) + (size_t)m * p.n + c0;
   float ss = 0.f;
+  // parts whose rows start on 16 bytes: four entries per lane and load
+  const bool vec = sizeof(T) == 2 && (len & 3) == 0 && (p.n & 3) == 0 && (p.ldg & 3) == 0 &&
+                   (((uintptr_t)p.o | (uintptr_t)p.out) & 15) == 0 && (((uintptr_t)p.gate | (uintptr_t)(p.w ? p.w : p.gate)) & 7) == 0;
+  if (vec) {
+    const float4 *o4 = reinterpret_cast<const float4 *>(o);
+    const uint2 *g2 = reinterpret_cast<const uint2 *>(gate), *w2 = reinterpret_cast<const uint2 *>(w);
+    typedef typename Bits16<T>::type B;
+    for (int i = lane; i < len / 4; i += 32) {
+      const float4 ov = o4[i];
+      float v[4] = {ov.x, ov.y, ov.z, ov.w};
+      if (p.gate_first) {
+        const uint2 g = g2[i];
+        const float2 ga = DT<B>::unpack2(g.x), gb = DT<B>::unpack2(g.y);
+        v[0] *= silu_f(ga.x); v[1] *= silu_f(ga.y); v[2] *= silu_f(gb.x); v[3] *= silu_f(gb.y);
+      }
+      ss = fmaf(v[0], v[0], ss); ss = fmaf(v[1], v[1], ss); ss = fmaf(v[2], v[2], ss); ss = fmaf(v[3], v[3], ss);
+    }
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)len + p.eps);
+    for (int i = lane; i < len / 4; i += 32) {
+      const float4 ov = o4[i];
+      const uint2 g = g2[i];
+      const float2 ga = DT<B>::unpack2(g.x), gb = DT<B>::unpack2(g.y);
+      const float gs[4] = {silu_f(ga.x), silu_f(ga.y), silu_f(gb.x), silu_f(gb.y)};
+      float v[4] = {ov.x, ov.y, ov.z, ov.w};
+      float wv[4] = {1.f, 1.f, 1.f, 1.f};
+      if (w) {
+        const uint2 ww = w2[i];
+        const float2 wa = DT<B>::unpack2(ww.x), wb = DT<B>::unpack2(ww.y);
+        wv[0] = wa.x; wv[1] = wa.y; wv[2] = wb.x; wv[3] = wb.y;
+      }
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        float r = (p.gate_first ? v[e] * gs[e] : v[e]) * inv;
+        if (w) r *= wv[e];
+        if (!p.gate_first) r *= gs[e];
+        v[e] = r;
+      }
+      *reinterpret_cast<uint2 *>(out + 4 * i) = make_uint2(pack2x<B>(v[0], v[1]), pack2x<B>(v[2], v[3]));
+    }
+    return;
+  }
   for (int i = lane; i < len; i += 32) {
     const float v = p.gate_first ? o[i] * silu_f(DT<T>::to_f(gate[i])) : o[i];
     ss = fmaf(v, v, ss);
@@ -1070,6 +1124,26 @@ template <typename T>
 __global__ void __launch_bounds__(256) moe_combine_kernel(const MoeCombine p) {
   const int m = blockIdx.x;
   const T *h = reinterpret_cast<const T *>(p.h) + (size_t)m * p.W;
+  if ((p.W & 3) == 0) {  // 16-byte loads and stores of the fp32 rows
+    const float4 *x4 = reinterpret_cast<const float4 *>(p.x + (size_t)m * p.W);
+    float4 *o4 = reinterpret_cast<float4 *>(p.x_out + (size_t)m * p.W);
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < p.W / 4; i += gridDim.y * blockDim.x) {
+      float4 s = x4[i];
+      for (int k = 0; k < p.top; k++) {
+        const size_t pr = (size_t)m * p.top + k;
+        const float w = p.wts[pr];
+        if (p.ids[pr] < p.experts) {
+          const float4 y = reinterpret_cast<const float4 *>(p.y + (size_t)p.pos_of[pr] * p.W)[i];
+          s.x = fmaf(w, y.x, s.x); s.y = fmaf(w, y.y, s.y); s.z = fmaf(w, y.z, s.z); s.w = fmaf(w, y.w, s.w);
+        } else {
+          s.x = fmaf(w, DT<T>::to_f(h[4 * i]), s.x); s.y = fmaf(w, DT<T>::to_f(h[4 * i + 1]), s.y);
+          s.z = fmaf(w, DT<T>::to_f(h[4 * i + 2]), s.z); s.w = fmaf(w, DT<T>::to_f(h[4 * i + 3]), s.w);
+        }
+      }
+      o4[i] = s;
+    }
+    return;
+  }
   for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < p.W; i += gridDim.y * blockDim.x) {
     float s = 0.f;
     for (int k = 0; k < p.top; k++) {
